@@ -14,6 +14,7 @@
 #include "stack.hpp"
 #include "safetensors.hpp"
 #include "stack_kernels.cuh"
+#include "stack_kernels_mix.cuh"
 
 #include <algorithm>
 #include <cmath>
@@ -31,9 +32,9 @@ using namespace stk;
 
 namespace {
 
-enum MixerKind { MIX_MINGRU = 0, MIX_LATENT, MIX_DELTA, MIX_GDELTA, MIX_DIFFATTN };
-enum BlockKind { BLOCK_SEQUENTIAL = 0, BLOCK_PARALLEL };
-enum FfKind { FF_GLU = 0, FF_POLY };
+enum MixerKind { MIX_MINGRU = 0, MIX_LATENT, MIX_DELTA, MIX_GDELTA, MIX_DIFFATTN, MIX_RETENTION, MIX_SIGATTN, MIX_PAIR };
+enum BlockKind { BLOCK_SEQUENTIAL = 0, BLOCK_PARALLEL, BLOCK_PRENORM };
+enum FfKind { FF_GLU = 0, FF_POLY, FF_MOE };
 constexpr int CHUNK_MAX = 512;          // tokens per pass of a prompt portion (longer steps run as several passes)
 constexpr float GLU_ALPHA = 1.702f;     // the feed-forward's sigmoid slope: fixed by the design
 
@@ -74,8 +75,29 @@ struct LayerSpec {
     // feed-forward
     int ff = 0, ff_kind = FF_GLU;
     float limit = 0.f;
-    DMat gateup, down;                   // FF_POLY: gateup is the plain up-projection
+    DMat gateup, down;                   // FF_POLY: gateup is the plain up-projection; FF_MOE: the shared unit (ff = 0: none)
     float * act = nullptr;               // FF_POLY: the four coefficients
+    // FF_MOE: routed mixture of gated units. e_gateup [n_exp][2 e_ff][E] (gate / up interleaved), e_down [n_exp][E][e_ff]
+    int n_exp = 0, top = 0, n_groups = 1, keep_groups = 1, e_ff = 0;
+    float r_scale = 1.f;
+    float * router = nullptr, * w_sg = nullptr;      // float32: the router is computed in 32-bit
+    DMat e_gateup, e_down;
+    // element-wise norms (dynamic tanh): weight in norm1 / norm2, bias and slope here
+    float * n1_b = nullptr, * n2_b = nullptr;
+    float n1_alpha = 1.f, n2_alpha = 1.f;
+    // depth average after the layer: coefficients over the embedding output and every layer's result so far
+    float * dwa = nullptr;
+    int n_dwa = 0;
+    // retention: constant decay per head; rotation of q and k (rope_freq / rope_dims above)
+    float * decay = nullptr;
+    float k_scale = 1.f;
+    // sigmoid attention: weights of the whole-projection norms, per-head score offset and distance slope, query temperature
+    float * qw = nullptr, * kw = nullptr, * pb = nullptr, * slope = nullptr;
+    float t_coef = 0.f;
+    int t_every = 0;
+    // a pair of mixers side by side (MIX_PAIR): each over its root mean square times a weight, then their mean
+    std::vector<LayerSpec> parts;
+    float * pair_w[2] = { nullptr, nullptr };
     // parallel blocks: weights of the causal convolution in front of each sub-layer, [2][E][taps]
     float * canon = nullptr;
     // state a sequence keeps for one run of this layer
@@ -101,6 +123,12 @@ struct StackModel {
     int block = BLOCK_SEQUENTIAL;
     int canon_taps = 0;                   // parallel blocks: taps of the input convolutions (0: none)
     float softcap = 0.f;                  // > 0: logits <- cap tanh(logits / cap)
+    bool dyt = false;                     // the model's norm is the element-wise dynamic tanh (weight, bias, slope)
+    float * embed_w = nullptr, * embed_b = nullptr, * final_b = nullptr;
+    float embed_alpha = 1.f, final_alpha = 1.f;
+    bool depth_avg = false;               // every layer hands on a weighted sum of all results so far
+    bool has_pair = false;
+    int max_slots = 0, max_eff = 0, max_exp = 0;      // routed mixtures: choices per token, expert width, experts
     DMat loop_in;                         // repeated span: [E][2 E]
     float * loop_step = nullptr;          // [times][E]
     std::vector<LayerSpec> layers;
@@ -149,7 +177,10 @@ struct StackCtx {
     size_t att_scores_floats = 0;
     std::vector<float *> cache_allocs;    // the caches with their zero margins (caches[] point behind the front margin)
     float * att_part = nullptr, * att_ml = nullptr;   // key-slice partials of the latent attention (decode)
-    float * da_part = nullptr;            // key-slice partials of the differential attention (few-token steps)
+    float * keep = nullptr;               // depth average: [layers + 1][cap][E] results of this pass's tokens
+    float * Xp = nullptr, * Ap = nullptr, * Yk = nullptr, * r_wt = nullptr, * r_sg = nullptr;      // routed mixture: rows by slot, weights, shared gate
+    int32_t * r_sel = nullptr, * r_slot = nullptr, * r_src = nullptr, * r_seg = nullptr;
+    float * da_part = nullptr;            // key-slice partials of the differential / sigmoid attention (few-token steps)
     int * da_counter = nullptr;           // per (token, head): slices done
     int sm_count = 148;
     __nv_bfloat16 * xb = nullptr;         // activations of a prompt pass rounded to bfloat16 (operand of the tcgen05 product)
@@ -384,6 +415,75 @@ void load_diffattn(StackModel & m, LayerSpec & L, const Json & mx, const safeten
     m.maxQK = std::max(m.maxQK, nq); m.maxOL = std::max(m.maxOL, H * V);      // prompt portions: regrouped queries, per-group outputs
 }
 
+// plain rotary frequencies f_i = base^(-2i/dims) of a mixer's "rot" object (absent: no rotation)
+void load_rot(StackModel & m, LayerSpec & L, const Json & mx, int D) {
+    L.rope_dims = 0; L.rope_mag = 1.f;
+    std::vector<float> freq(1, 0.f);
+    if (mx.has("rot")) {
+        const Json & rot = mx.at("rot");
+        const int dims = L.rope_dims = (int) rot.integer("dims", D);
+        if (dims < 0 || dims > D || dims % 2) throw std::runtime_error("config: rot.dims must be even and at most dim");
+        const double base = rot.number("base");
+        freq.assign((size_t) std::max(dims / 2, 1), 0.f);
+        for (int i = 0; i < dims / 2; i++) freq[(size_t) i] = (float) std::pow(base, -2.0 * i / dims);
+    }
+    L.rope_freq = up_f32(m, freq);
+}
+
+// retention: '<prefix>{q,k,v,g,o}'; decay per head from the configuration
+void load_retention(StackModel & m, LayerSpec & L, const Json & mx, const safetensors_file & sf, const std::string & p) {
+    const int E = m.E;
+    const int H = L.H = need_int(mx, "heads"), D = L.D = need_int(mx, "dim"), V = L.V = need_int(mx, "vdim");
+    if (D > 256) throw std::runtime_error("retention: dim above 256 is not supported by the recurrence kernel");
+    const Json & dj = mx.at("decay");
+    if (dj.kind != Json::Arr || (int) dj.arr.size() != H) throw std::runtime_error("config: 'decay' must list one number per head");
+    std::vector<float> dec((size_t) H);
+    for (int h = 0; h < H; h++) { if (dj.arr[(size_t) h].kind != Json::Num) throw std::runtime_error("config: 'decay' must hold numbers"); dec[(size_t) h] = (float) dj.arr[(size_t) h].num; }
+    L.decay = up_f32(m, dec);
+    load_rot(m, L, mx, D);
+    L.k_scale = (float) (1.0 / std::sqrt((double) D));
+    std::vector<float> W = sf.read_f32(p + "q", {H * D, E});
+    append(W, sf.read_f32(p + "k", {H * D, E}));
+    append(W, sf.read_f32(p + "v", {H * V, E}));
+    append(W, sf.read_f32(p + "g", {H * V, E}));
+    L.proj = up_mat(m, W, 2 * H * D + 2 * H * V, E, nullptr);
+    L.o = up_mat(m, sf.read_f32(p + "o", {E, H * V}), E, H * V, nullptr);
+    L.n_rec = (size_t) H * D * V;
+    m.maxP = std::max(m.maxP, L.proj.N); m.maxA = std::max(m.maxA, H * V);
+}
+
+// sigmoid attention: '<prefix>{q,k,v,q.norm,k.norm,pb,o}'; slopes 2^(-8 (h + 1) / H) are fixed by the mechanism
+void load_sigattn(StackModel & m, LayerSpec & L, const Json & mx, const safetensors_file & sf, const std::string & p) {
+    const int E = m.E;
+    const int H = L.H = need_int(mx, "heads"), G = L.KH = (int) mx.integer("kv_heads", H), D = L.D = need_int(mx, "dim"), V = L.V = need_int(mx, "vdim");
+    if (G < 1 || H % G) throw std::runtime_error("config: attention heads must be a multiple of kv_heads");
+    if (V > 256 || D > 256) throw std::runtime_error("sigmoid attention: dim and vdim above 256 are not supported by the attention kernel");
+    L.scale = (float) mx.number("scale");
+    if (mx.has("q_temp")) {
+        L.t_coef = (float) mx.at("q_temp").number("coef");
+        L.t_every = need_int(mx.at("q_temp"), "every");
+    }
+    std::vector<float> W = sf.read_f32(p + "q", {H * D, E});
+    append(W, sf.read_f32(p + "k", {G * D, E}));
+    append(W, sf.read_f32(p + "v", {G * V, E}));
+    L.proj = up_mat(m, W, H * D + G * D + G * V, E, nullptr);
+    L.qw = up_f32(m, sf.read_f32(p + "q.norm", {H * D}));
+    L.kw = up_f32(m, sf.read_f32(p + "k.norm", {G * D}));
+    L.pb = up_f32(m, sf.read_f32(p + "pb", {H}));
+    std::vector<float> sl((size_t) H);
+    for (int h = 0; h < H; h++) sl[(size_t) h] = (float) std::exp2(-8.0 * (h + 1) / H);
+    L.slope = up_f32(m, sl);
+    L.o = up_mat(m, sf.read_f32(p + "o", {E, H * V}), E, H * V, nullptr);
+    L.cache_row = (size_t) G * D + (size_t) G * V;
+    m.maxP = std::max(m.maxP, L.proj.N); m.maxA = std::max(m.maxA, H * V);
+    m.maxCV = std::max(m.maxCV, H * D);
+    m.maxQK = std::max(m.maxQK, H * D); m.maxOL = std::max(m.maxOL, H * V);
+}
+
+struct MixerEntry;
+const MixerEntry & find_mixer(const std::string & type, size_t layer);
+void load_pair(StackModel & m, LayerSpec & L, const Json & mx, const safetensors_file & sf, const std::string & p);
+
 struct MixerEntry { const char * name; int kind; void (*load)(StackModel &, LayerSpec &, const Json &, const safetensors_file &, const std::string &); };
 const MixerEntry MIXERS[] = {
     { "mingru", MIX_MINGRU, load_mingru },
@@ -391,11 +491,42 @@ const MixerEntry MIXERS[] = {
     { "delta", MIX_DELTA, load_delta },
     { "general_delta", MIX_GDELTA, load_gdelta },
     { "attention", MIX_DIFFATTN, load_diffattn },
+    { "retention", MIX_RETENTION, load_retention },
+    { "sigmoid_attention", MIX_SIGATTN, load_sigattn },
+    { "parallel", MIX_PAIR, load_pair },
 };
 
 const MixerEntry & find_mixer(const std::string & type, size_t layer) {
     for (const MixerEntry & e : MIXERS) if (type == e.name) return e;
     throw std::runtime_error("config: layer " + std::to_string(layer) + " has unknown mixer type '" + type + "'");
+}
+
+// two mixers side by side on the same input: '<prefix>left.*' and '<prefix>right.*', each branch's output over its root mean
+// square times '<prefix>left.out' / '<prefix>right.out', then their mean. A branch names its mixer by "type" (absent: a sigmoid
+// attention on the left, a retention on the right).
+void load_pair(StackModel & m, LayerSpec & L, const Json & mx, const safetensors_file & sf, const std::string & p) {
+    const char * side[2] = { "left", "right" }, * dflt[2] = { "sigmoid_attention", "retention" };
+    L.parts.resize(2);
+    L.n_rec = 0; L.cache_row = 0;
+    for (int i = 0; i < 2; i++) {
+        const Json & bj = mx.at(side[i]);
+        const MixerEntry & me = find_mixer(bj.string("type", dflt[i]), 0);
+        if (me.kind == MIX_PAIR) throw std::runtime_error("config: a branch of a parallel mixer cannot be a parallel mixer");
+        LayerSpec & B = L.parts[(size_t) i];
+        B.kind = me.kind;
+        me.load(m, B, bj, sf, p + side[i] + ".");
+        L.pair_w[i] = up_f32(m, sf.read_f32(p + side[i] + ".out", {m.E}));
+        L.n_rec += (B.n_rec + 3) / 4 * 4;
+    }
+    m.has_pair = true;
+}
+
+// the attention caches one run of a layer needs (a pair: its branches')
+int n_layer_caches(const LayerSpec & L) {
+    if (L.kind != MIX_PAIR) return L.cache_row ? 1 : 0;
+    int n = 0;
+    for (const LayerSpec & B : L.parts) n += B.cache_row ? 1 : 0;
+    return n;
 }
 
 // one run of `layer`: its slice of the recurrent slab and, for attention, a cache of its own
@@ -405,7 +536,7 @@ void add_run(StackModel & m, int layer, int pass) {
     r.layer = layer; r.pass = pass;
     r.off_rec = m.rec_floats;
     m.rec_floats += (L.n_rec + 3) / 4 * 4;
-    if (L.cache_row) r.cache_index = m.n_caches++;
+    if (const int nc = n_layer_caches(L)) { r.cache_index = m.n_caches; m.n_caches += nc; }
     m.weight_bytes += L.bytes;
     m.runs.push_back(r);
 }
@@ -544,10 +675,110 @@ void build_dopilorn(StackModel & m, const Json & cfg, const safetensors_file & s
     m.head = up_mat(m, sf.read_f32("head", {m.vocab, E}), m.vocab, E, nullptr);
 }
 
+// Tosevik: x0 = dyt(embed) -> layers (y = z + mixer(dyt1 z); y += mixture(dyt2 y) when the layer has a feed-forward; the next layer
+// reads z = sum_j dwa[j] x_j over the embedding output and all results so far) -> dyt -> head. Norms are element-wise (dynamic
+// tanh: weight, bias '.b', slope '.alpha'). Mixers: retention | parallel (sigmoid attention beside retention).
+float read_scalar(const safetensors_file & sf, const std::string & name) {
+    const st_tensor * t = sf.find(name);
+    if (!t || t->numel() != 1) throw std::runtime_error("tensor " + name + " is missing or not a single number");
+    return sf.read_f32(name, t->shape)[0];
+}
+DMat load_glu_pair(StackModel & m, const safetensors_file & sf, const std::string & p, int ff, int E, std::vector<float> * into) {
+    // gate and up interleaved row by row (2i: gate_i, 2i + 1: up_i): the product's epilogue holds both halves of a unit
+    const std::vector<float> Wg = sf.read_f32(p + "gate", {ff, E}), Wu = sf.read_f32(p + "up", {ff, E});
+    std::vector<float> W((size_t) 2 * ff * E);
+    for (int i = 0; i < ff; i++) {
+        std::memcpy(&W[(size_t) (2 * i) * E], &Wg[(size_t) i * E], (size_t) E * 4);
+        std::memcpy(&W[(size_t) (2 * i + 1) * E], &Wu[(size_t) i * E], (size_t) E * 4);
+    }
+    if (into) { append(*into, W); return DMat(); }
+    return up_mat(m, W, 2 * ff, E, nullptr);
+}
+void load_mixture(StackModel & m, LayerSpec & L, const Json & mj, const safetensors_file & sf, const std::string & p) {
+    const int E = m.E;
+    const Json & rj = mj.at("router");
+    const int n = L.n_exp = need_int(rj, "experts"), top = L.top = need_int(rj, "top");
+    L.r_scale = (float) rj.number("scale", 1.0);
+    L.n_groups = rj.has("groups") ? need_int(rj.at("groups"), "count") : 1;
+    L.keep_groups = rj.has("groups") ? need_int(rj.at("groups"), "keep") : 1;
+    if (n % L.n_groups) throw std::runtime_error("config: experts must be a multiple of groups.count");
+    if (L.keep_groups > L.n_groups) throw std::runtime_error("config: groups.keep exceeds groups.count");
+    if (top > L.keep_groups * (n / L.n_groups)) throw std::runtime_error("config: router.top exceeds the experts of the kept groups");
+    if (n > 4096 || top > 64) throw std::runtime_error("config: more than 4096 experts or 64 choices per token are not supported");
+    const int ff = L.e_ff = need_int(mj.at("expert"), "ff");
+    L.ff_kind = FF_MOE;
+    L.router = up_f32(m, sf.read_f32(p + "router", {n, E}));
+    std::vector<float> GU, DN;
+    for (int e = 0; e < n; e++) {
+        const std::string ep = p + "e" + std::to_string(e) + ".";
+        load_glu_pair(m, sf, ep, ff, E, &GU);
+        append(DN, sf.read_f32(ep + "down", {E, ff}));
+    }
+    const int64_t before = m.weight_bytes;
+    L.e_gateup = up_mat(m, GU, 2 * ff, E, nullptr, n);
+    L.e_down = up_mat(m, DN, E, ff, nullptr, n);
+    m.weight_bytes = before + (m.weight_bytes - before) / n * top + (int64_t) n * E * 4;      // a token reads its chosen experts and the router
+    L.ff = 0;
+    if (mj.has("shared")) {
+        const int sff = L.ff = need_int(mj.at("shared"), "ff");
+        L.gateup = load_glu_pair(m, sf, p + "shared.", sff, E, nullptr);
+        L.down = up_mat(m, sf.read_f32(p + "shared.down", {E, sff}), E, sff, nullptr);
+        L.w_sg = up_f32(m, sf.read_f32(p + "shared.sg", {1, E}));
+        m.maxA = std::max(m.maxA, sff);
+    }
+    m.max_slots = std::max(m.max_slots, top); m.max_eff = std::max(m.max_eff, ff); m.max_exp = std::max(m.max_exp, n);
+}
+void build_tosevik(StackModel & m, const Json & cfg, const safetensors_file & sf) {
+    m.block = BLOCK_PRENORM;
+    m.dyt = true; m.depth_avg = true;
+    m.vocab = need_int(cfg, "vocab"); m.E = need_int(cfg, "width");
+    m.eps = (float) cfg.at("norm").number("eps");
+    m.groups = 1;
+    const int E = m.E;
+    {
+        DMat d = up_mat(m, sf.read_f32("embed", {m.vocab, E}), m.vocab, E, nullptr);
+        m.embed = d.w;
+        m.weight_bytes -= d.bytes;
+    }
+    m.embed_w = up_f32(m, sf.read_f32("embed.norm", {E})); m.embed_b = up_f32(m, sf.read_f32("embed.norm.b", {E})); m.embed_alpha = read_scalar(sf, "embed.norm.alpha");
+    const Json & layers = cfg.at("layers");
+    if (layers.kind != Json::Arr || layers.arr.empty()) throw std::runtime_error("config: 'layers' must be a non-empty list");
+    const int n = (int) layers.arr.size();
+    for (int i = 0; i < n; i++) {
+        const Json & lj = layers.arr[(size_t) i];
+        const std::string type = lj.string("type", ""), p = "l" + std::to_string(i) + ".";
+        const MixerEntry * me = &find_mixer(type, (size_t) i);
+        if (me->kind != MIX_RETENTION && me->kind != MIX_PAIR) throw std::runtime_error("config: mixer '" + type + "' is not part of the Tosevik design");
+        const int64_t bytes0 = m.weight_bytes;
+        m.layers.emplace_back();
+        LayerSpec & L = m.layers.back();
+        L.kind = me->kind;
+        L.has_mlp = lj.has("mlp");
+        L.norm1 = up_f32(m, sf.read_f32(p + "norm1", {E})); L.n1_b = up_f32(m, sf.read_f32(p + "norm1.b", {E})); L.n1_alpha = read_scalar(sf, p + "norm1.alpha");
+        me->load(m, L, lj.at("mixer"), sf, p + "mix.");
+        if (L.has_mlp) {
+            const Json & mj = lj.at("mlp");
+            const std::string kind = mj.string("kind", "moe");
+            if (kind != "moe") throw std::runtime_error("config: feed-forward kind '" + kind + "' is not part of the Tosevik design (moe)");
+            L.norm2 = up_f32(m, sf.read_f32(p + "norm2", {E})); L.n2_b = up_f32(m, sf.read_f32(p + "norm2.b", {E})); L.n2_alpha = read_scalar(sf, p + "norm2.alpha");
+            load_mixture(m, L, mj, sf, p + "mlp.");
+        }
+        L.n_dwa = i + 2;
+        L.dwa = up_f32(m, sf.read_f32(p + "dwa", {i + 2}));
+        m.weight_bytes += (int64_t) E * 4 * (L.has_mlp ? 4 : 2);
+        L.bytes = m.weight_bytes - bytes0;
+        m.weight_bytes = bytes0;
+        add_run(m, i, -1);
+    }
+    m.final_norm = up_f32(m, sf.read_f32("final.norm", {E})); m.final_b = up_f32(m, sf.read_f32("final.norm.b", {E})); m.final_alpha = read_scalar(sf, "final.norm.alpha");
+    m.head = up_mat(m, sf.read_f32("head", {m.vocab, E}), m.vocab, E, nullptr);
+}
+
 struct DesignEntry { const char * name; void (*build)(StackModel &, const Json &, const safetensors_file &); };
 const DesignEntry DESIGNS[] = {
     { "Matulorn", build_matulorn },
     { "Dopilorn", build_dopilorn },
+    { "Tosevik", build_tosevik },
 };
 
 // ---- launches ---------------------------------------------------------------------------------------------------------
@@ -564,11 +795,21 @@ bool umma_enabled() {
 // bounded waits raise
 struct UmmaScratch { __nv_bfloat16 * xb = nullptr; size_t elems = 0; int * err = nullptr; };
 
+// what a product may ask for beyond its operands: the gated unit's constants (y = g sigmoid(alpha g) (u + shift), g and u clamped
+// at +-limit), rows sorted into segments per batch entry (tile kernels), an indexed batch (mat-vec)
+struct LinOpt {
+    float alpha = GLU_ALPHA, shift = 1.f;
+    const int32_t * seg = nullptr;
+    const int32_t * w_index = nullptr;
+    int x_share = 1;
+};
 void linear_on(cudaStream_t st, int dtype, int64_t * launches, const float * X, int ldx, const void * W, const float * bias, float * Y, int ldy,
                int T, int N, int K, int batch = 1, long long sX = 0, long long sW = 0, long long sY = 0, bool glu = false, float glu_limit = 0.f,
-               const UmmaScratch * us = nullptr) {
+               const UmmaScratch * us = nullptr, const LinOpt * opt = nullptr) {
     if (T <= 0 || N <= 0) return;
     LinArgs a{X, W, bias, Y, T, N, K, ldx, ldy, sX, sW, sY, 0, glu ? 1 : 0, glu_limit, GLU_ALPHA, 0, 0};
+    if (opt) { a.alpha = opt->alpha; a.up_shift = opt->shift; a.seg = opt->seg; a.w_index = opt->w_index; a.x_share = opt->x_share; }
+    const int xbatch = a.seg ? 1 : batch;      // segments: X is one matrix of T rows
     const int vecw = dtype == STACK_F32 ? 4 : 8;
     const auto al16 = [](const void * p) { return ((uintptr_t) p & 15) == 0; };
     a.vec = K % vecw == 0 && ldx % 4 == 0 && sX % 4 == 0 && sW % vecw == 0 && al16(X) && al16(W);
@@ -581,11 +822,11 @@ void linear_on(cudaStream_t st, int dtype, int64_t * launches, const float * X, 
             const dim3 grid((unsigned) ((N + 7) / 8), 1, (unsigned) batch);
             if (dtype == STACK_F32) k_gemv<float, 1><<<grid, 256, 0, st>>>(a); else k_gemv<__nv_bfloat16, 1><<<grid, 256, 0, st>>>(a);
         }
-    } else if (dtype == STACK_BF16 && a.vec && us && us->xb && umma_enabled() && T >= 64 && N >= 128 && K >= 64 && (size_t) batch * T * K <= us->elems) {
+    } else if (dtype == STACK_BF16 && a.vec && us && us->xb && umma_enabled() && T >= 64 && N >= 128 && K >= 64 && (size_t) xbatch * T * K <= us->elems) {
         // tensor memory path: activations to bfloat16 once, then tcgen05.mma over cp.async-fed stages
         static const bool attr = [] { return cudaFuncSetAttribute(k_gemm_bf16_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_SMEM) == cudaSuccess; }();
         if (!attr) throw std::runtime_error("cannot reserve shared memory for k_gemm_bf16_umma");
-        k_to_bf16<<<dim3((unsigned) std::min((K + 255) / 256, 64), (unsigned) T, (unsigned) batch), 256, 0, st>>>(X, ldx, T, K, sX, us->xb, (long long) T * K);
+        k_to_bf16<<<dim3((unsigned) std::min((K + 255) / 256, 64), (unsigned) T, (unsigned) xbatch), 256, 0, st>>>(X, ldx, T, K, sX, us->xb, (long long) T * K);
         const dim3 grid((unsigned) ((N + UM_BN - 1) / UM_BN), (unsigned) ((T + UM_BM - 1) / UM_BM), (unsigned) batch);
         k_gemm_bf16_umma<<<grid, 256, UM_SMEM, st>>>(a, us->xb, (long long) T * K, us->err);
         if (launches) (*launches)++;
@@ -599,9 +840,10 @@ void linear_on(cudaStream_t st, int dtype, int64_t * launches, const float * X, 
     SCU(cudaGetLastError());
 }
 
-void linear(StackCtx * c, const float * X, int ldx, const DMat & W, float * Y, int ldy, int T, int batch = 1, long long sX = 0, long long sY = 0, bool glu = false, float glu_limit = 0.f) {
+void linear(StackCtx * c, const float * X, int ldx, const DMat & W, float * Y, int ldy, int T, int batch = 1, long long sX = 0, long long sY = 0, bool glu = false, float glu_limit = 0.f,
+            const LinOpt * opt = nullptr) {
     const UmmaScratch us{c->xb, c->xb_elems, c->d_err};
-    linear_on(c->st, c->m->dtype, &c->launches, X, ldx, W.w, W.bias, Y, ldy, T, W.N, W.K, batch, sX, (long long) W.N * W.K, sY, glu, glu_limit, &us);
+    linear_on(c->st, c->m->dtype, &c->launches, X, ldx, W.w, W.bias, Y, ldy, T, W.N, W.K, batch, sX, (long long) W.N * W.K, sY, glu, glu_limit, &us, opt);
 }
 
 // end of a sub-layer: X += norm(Y) * w_post; Hn = norm(X) * w_next when another sub-layer follows
@@ -857,13 +1099,107 @@ void mixer_diffattn(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T)
     linear(c, c->A, H * V, L.o, c->out, E, T);
 }
 
+template <int DMAX>
+void launch_retention_scan(StackCtx * c, const LayerSpec & L, int T, int ldp, float * S) {
+    // four lanes per column of the state; a head's columns are spread over blocks of >= 16 until the grid fills the SMs
+    int ncols = std::min(128, (L.V + 7) / 8 * 8);
+    while (ncols > 16 && L.H * ((L.V + ncols - 1) / ncols) < c->sm_count) ncols = (ncols / 2 + 7) / 8 * 8;
+    const int HD = L.H * L.D;
+    const dim3 grid((unsigned) L.H, (unsigned) ((L.V + ncols - 1) / ncols));
+    k_retention_scan<DMAX><<<grid, GD_RG * ncols, 0, c->st>>>(c->P, ldp, 0, HD, 2 * HD, L.decay, T, L.H, L.D, L.V, S, c->O);
+}
+
+// retention: P[t] = [ q | k | v | gate ] -> rotation, key scale -> recurrence -> per-head unit norm, silu gate -> output product
+void mixer_retention(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) {
+    const int E = c->m->E, H = L.H, D = L.D, V = L.V, HD = H * D, HV = H * V, ldp = L.proj.N;
+    float * S = c->rec + R.off_rec;
+    linear(c, c->in, E, L.proj, c->P, ldp, T);
+    k_retention_prep<<<T, 128, 0, c->st>>>(c->P, ldp, 0, HD, H, D, RopeArgs{L.rope_freq, L.rope_dims, 1.0f}, L.k_scale, &c->d_step->st);
+    if (D <= 32) launch_retention_scan<32>(c, L, T, ldp, S);
+    else if (D <= 64) launch_retention_scan<64>(c, L, T, ldp, S);
+    else if (D <= 128) launch_retention_scan<128>(c, L, T, ldp, S);
+    else launch_retention_scan<256>(c, L, T, ldp, S);
+    k_delta_out<<<dim3((unsigned) T, (unsigned) ((H + 3) / 4)), 128, 0, c->st>>>(c->O, c->P, ldp, 2 * HD + HV, H, V, nullptr, 0, 0, c->m->eps, c->A);
+    c->launches += 3;
+    linear(c, c->A, HV, L.o, c->out, E, T);
+}
+
+constexpr int SIG_MAX_SPLIT = 16;
+int sig_vpl(const LayerSpec & L) { return L.V <= 32 ? 1 : L.V <= 64 ? 2 : L.V <= 128 ? 4 : 8; }
+
+// sigmoid attention: P[t] = [ q | k | v ] -> norms, temperature; keys and values to the cache row of the token's position ->
+// weights sigmoid(score - slope distance + offset) over all earlier positions -> output product
+void mixer_sigattn(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) {
+    const int E = c->m->E, H = L.H, G = L.KH, D = L.D, V = L.V, nq = H * D, row = (int) L.cache_row;
+    float * cache = c->caches[(size_t) R.cache_index];
+    linear(c, c->in, E, L.proj, c->P, L.proj.N, T);
+    k_sigattn_prep<<<T, 256, 0, c->st>>>(c->P, L.proj.N, H, G, D, V, L.qw, L.kw, c->m->eps, L.t_coef, L.t_every, &c->d_step->st, c->CV, cache);
+    c->launches++;
+    if (T >= 8) {
+        // prompt portion: float32 products over tiles of ATT_TQ tokens, one batch entry per (tile, key/value head)
+        const int TQ = ATT_TQ, Rh = H / G, M = TQ * Rh, ntile = (T + TQ - 1) / TQ, Tpad = ntile * TQ;
+        const int pos0 = c->h_step->st.pos0;
+        k_group_q_layout<<<Tpad, 256, 0, c->st>>>(c->CV, nq, T, Tpad, H, G, D, c->QK);
+        const size_t nk_max = (size_t) (pos0 + Tpad + 3) / 4 * 4;
+        const int per_group = (int) std::max<size_t>(1, c->att_scores_floats / ((size_t) G * M * nk_max));
+        for (int g0 = 0; g0 < ntile; g0 += per_group) {
+            const int ng = std::min(per_group, ntile - g0);
+            const int nk = (pos0 + (g0 + ng) * TQ + 3) / 4 * 4;                                           // no key beyond this group's last token is seen
+            const long long grp = (long long) ng * M * nk;
+            gemm_f32(c, c->QK + (size_t) g0 * M * D, D, (long long) M * D, cache, 0, row, 0, c->att_scores, nk, (long long) M * nk, M, nk, D, ng,
+                     G, (long long) Tpad * Rh * D, D, grp);
+            const int rows = ng * M * G;
+            k_sig_weight_rows<<<(rows + 7) / 8, 256, 0, c->st>>>(c->att_scores, ng * M, G, Rh, TQ, nk, &c->d_step->st, L.scale, L.slope, L.pb, g0, T);
+            gemm_f32(c, c->att_scores, nk, (long long) M * nk, cache + (size_t) G * D, 1, row, 0, c->OL + (size_t) g0 * M * V, V, (long long) M * V, M, V, nk, ng,
+                     G, grp, V, (long long) Tpad * Rh * V);
+            c->launches++;
+        }
+        k_group_o_layout<<<T, 256, 0, c->st>>>(c->OL, Tpad, H, G, V, c->A);
+        c->launches += 2;
+        linear(c, c->A, H * V, L.o, c->out, E, T);
+        return;
+    }
+    const int TQ = T >= 4 ? 4 : T >= 2 ? 2 : 1, WPQ = 8 / TQ;
+    const int blocks = ((T + TQ - 1) / TQ) * H;
+    const int nsplit = std::max(1, std::min({ 2 * c->sm_count / blocks, ((c->n_ctx + 31) / 32 + WPQ - 1) / WPQ, SIG_MAX_SPLIT }));
+    SigAttnArgs a{c->CV, nq, cache, row, &c->d_step->st, c->A, L.slope, L.pb, T, H, G, D, V, L.scale, TQ,
+                  (D % 4 == 0 && row % 4 == 0 && ((uintptr_t) cache & 15) == 0) ? 1 : 0, nsplit, c->da_part, c->da_counter};
+    const dim3 grid((unsigned) ((T + TQ - 1) / TQ), (unsigned) H, (unsigned) nsplit);
+    const int VPL = sig_vpl(L);
+    const size_t smem = ((size_t) TQ * D + (size_t) 8 * 32 * VPL) * 4;
+    if (VPL == 1) k_sig_attn<1><<<grid, 256, smem, c->st>>>(a);
+    else if (VPL == 2) k_sig_attn<2><<<grid, 256, smem, c->st>>>(a);
+    else if (VPL == 4) k_sig_attn<4><<<grid, 256, smem, c->st>>>(a);
+    else k_sig_attn<8><<<grid, 256, smem, c->st>>>(a);
+    c->launches++;
+    linear(c, c->A, H * V, L.o, c->out, E, T);
+}
+
 void tap_layer(StackCtx * c, size_t ri, int T) {
     const size_t E = (size_t) c->m->E, n = (size_t) T * E;
     SCU(cudaMemcpyAsync(c->tap_data.data() + ri * n, c->X, n * 4, cudaMemcpyDeviceToHost, c->st));
 }
 
+void run_mixer(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T);
+// two mixers on the same input: the first leaves its output in c->out, the second in c->Y2 (the layer's join norms and averages them)
+void mixer_pair(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) {
+    float * out = c->out;
+    RunSpec B = R;
+    for (size_t i = 0; i < L.parts.size(); i++) {
+        const LayerSpec & P = L.parts[i];
+        c->out = i == 0 ? out : c->Y2;
+        run_mixer(c, P, B, T);
+        B.off_rec += (P.n_rec + 3) / 4 * 4;
+        if (P.cache_row) B.cache_index++;
+    }
+    c->out = out;
+}
+
 void run_mixer(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) {
     switch (L.kind) {
+        case MIX_RETENTION: mixer_retention(c, L, R, T); break;
+        case MIX_SIGATTN:   mixer_sigattn(c, L, R, T); break;
+        case MIX_PAIR:      mixer_pair(c, L, R, T); break;
         case MIX_MINGRU:   mixer_mingru(c, L, R, T); break;
         case MIX_LATENT:   mixer_latent(c, L, R, T); break;
         case MIX_DELTA:    mixer_delta(c, L, R, T); break;
@@ -958,15 +1294,97 @@ void enqueue_layers_parallel(StackCtx * c, int T) {
     SCU(cudaGetLastError());
 }
 
+// routed mixture on c->Hn: the chosen experts' outputs by slot in c->Yk (slot order in *slot_of: nullptr = t top + k), the
+// shared unit's in c->Y; the layer's join weighs and adds them
+void mixture_ff(StackCtx * c, const LayerSpec & L, int T, const int32_t ** slot_of) {
+    const int E = c->m->E, top = L.top, ff = L.e_ff, slots = T * top;
+    const RouteArgs ra{c->Hn, E, E, L.router, L.w_sg, L.n_exp, top, L.n_groups, L.keep_groups, L.r_scale, c->r_sel, c->r_wt, c->r_sg};
+    k_moe_route<<<T, 256, (size_t) (2 * L.n_exp + L.n_groups) * 4, c->st>>>(ra);
+    c->launches++;
+    LinOpt o;
+    o.alpha = 1.f; o.shift = 0.f;               // silu(gate) * up, no clamp
+    if (T <= GEMV_MAX_T) {
+        // few tokens: one mat-vec per (token, choice) against the chosen expert's matrices
+        o.w_index = c->r_sel; o.x_share = top;
+        linear(c, c->Hn, E, L.e_gateup, c->Ap, ff, 1, slots, E, ff, true, INFINITY, &o);
+        o.x_share = 1;
+        linear(c, c->Ap, ff, L.e_down, c->Yk, E, 1, slots, ff, E, false, 0.f, &o);
+        *slot_of = nullptr;
+    } else {
+        // prompt portion: rows sorted by expert, one segmented product per projection
+        k_moe_sort<<<1, 256, (size_t) L.n_exp * 4, c->st>>>(c->r_sel, slots, top, L.n_exp, c->r_seg, c->r_slot, c->r_src);
+        k_gather_rows<<<slots, 128, 0, c->st>>>(c->Hn, E, c->r_src, E, c->Xp);
+        c->launches += 2;
+        o.seg = c->r_seg;
+        linear(c, c->Xp, E, L.e_gateup, c->Ap, ff, slots, L.n_exp, 0, 0, true, INFINITY, &o);
+        linear(c, c->Ap, ff, L.e_down, c->Yk, E, slots, L.n_exp, 0, 0, false, 0.f, &o);
+        *slot_of = c->r_slot;
+    }
+    if (L.ff > 0) {
+        LinOpt s;
+        s.alpha = 1.f; s.shift = 0.f;
+        linear(c, c->Hn, E, L.gateup, c->A, L.ff, T, 1, 0, 0, true, INFINITY, &s);
+        linear(c, c->A, L.ff, L.down, c->Y, E, T);
+    }
+}
+
+// pre-norm blocks with element-wise norms: y = z + mixer(dyt1 z); y += ff(dyt2 y); the next layer reads the depth average of
+// the embedding output and all layers' y so far. Every sub-layer ends in one k_join launch that also norms the next one's input.
+void enqueue_layers_prenorm(StackCtx * c, int T) {
+    StackModel & m = *c->m;
+    const int E = m.E;
+    const long long plane = (long long) c->cap * E;
+    const dim3 jgrid((unsigned) T, (unsigned) ((E + JOIN_SLICE - 1) / JOIN_SLICE));
+    {
+        const LayerSpec & L0 = m.layers[(size_t) m.runs[0].layer];
+        const DytW ne{m.embed_w, m.embed_b, m.embed_alpha}, n1{L0.norm1, L0.n1_b, L0.n1_alpha};
+        if (m.dtype == STACK_F32) k_embed_dyt<float><<<T, 256, 0, c->st>>>((const float *) m.embed, c->d_step->tokens, E, m.vocab, ne, n1, c->X, m.depth_avg ? c->keep : nullptr, c->Hn);
+        else k_embed_dyt<__nv_bfloat16><<<T, 256, 0, c->st>>>((const __nv_bfloat16 *) m.embed, c->d_step->tokens, E, m.vocab, ne, n1, c->X, m.depth_avg ? c->keep : nullptr, c->Hn);
+        c->launches++;
+    }
+    for (size_t ri = 0; ri < m.runs.size(); ri++) {
+        const RunSpec & R = m.runs[ri];
+        const LayerSpec & L = m.layers[(size_t) R.layer];
+        const LayerSpec * N = ri + 1 < m.runs.size() ? &m.layers[(size_t) m.runs[ri + 1].layer] : nullptr;      // the final norm runs on the wanted rows only
+        c->in = c->Hn; c->out = c->Y;
+        run_mixer(c, L, R, T);
+        JoinArgs j{};
+        j.X = c->X; j.E = E; j.eps = m.eps; j.Ya = c->Y;
+        if (L.kind == MIX_PAIR) { j.Yb = c->Y2; j.wa = L.pair_w[0]; j.wb = L.pair_w[1]; }
+        const auto layer_end = [&](JoinArgs & a) {
+            if (m.depth_avg) { a.keep = c->keep; a.plane = plane; a.coef = L.dwa; a.n_keep = L.n_dwa; }
+            if (N) { a.nw = N->norm1; a.nb = N->n1_b; a.alpha = N->n1_alpha; a.Hn = c->Hn; }
+        };
+        if (L.has_mlp) { j.nw = L.norm2; j.nb = L.n2_b; j.alpha = L.n2_alpha; j.Hn = c->Hn; } else layer_end(j);
+        k_join<<<jgrid, 256, 0, c->st>>>(j);
+        c->launches++;
+        if (L.has_mlp) {
+            JoinArgs f{};
+            f.X = c->X; f.E = E; f.eps = m.eps;
+            mixture_ff(c, L, T, &f.slot_of);
+            f.Yk = c->Yk; f.wt = c->r_wt; f.top = L.top;
+            if (L.ff > 0) { f.Ysh = c->Y; f.sg = c->r_sg; }
+            layer_end(f);
+            k_join<<<jgrid, 256, 0, c->st>>>(f);
+            c->launches++;
+        }
+        if (c->taps) tap_layer(c, ri, T);
+    }
+    SCU(cudaGetLastError());
+}
+
 // the layers over the T tokens whose header (positions, ids) is already on the device
 void enqueue_layers(StackCtx * c, int T) {
-    if (c->m->block == BLOCK_PARALLEL) enqueue_layers_parallel(c, T); else enqueue_layers_sequential(c, T);
+    if (c->m->block == BLOCK_PARALLEL) enqueue_layers_parallel(c, T);
+    else if (c->m->block == BLOCK_PRENORM) enqueue_layers_prenorm(c, T);
+    else enqueue_layers_sequential(c, T);
 }
 
 // final norm + head on n_rows rows of the pass (row indices in d_step->rows) -> d_logits[row_off ..]
 void enqueue_head(StackCtx * c, int n_rows, int64_t row_off) {
     StackModel & m = *c->m;
-    norm(c, c->X, m.E, c->d_step->rows, m.final_norm, m.E, m.groups, c->Hn, m.E, n_rows, false);
+    if (m.dyt) { k_dyt_rows<<<n_rows, 256, 0, c->st>>>(c->X, m.E, c->d_step->rows, DytW{m.final_norm, m.final_b, m.final_alpha}, m.E, c->Hn, m.E); c->launches++; }
+    else norm(c, c->X, m.E, c->d_step->rows, m.final_norm, m.E, m.groups, c->Hn, m.E, n_rows, false);
     linear(c, c->Hn, m.E, m.head, c->d_logits + row_off * m.vocab, m.vocab, n_rows);
     if (m.softcap > 0.f) {
         const size_t n = (size_t) n_rows * m.vocab;
@@ -1060,7 +1478,8 @@ void stack_ctx_free(StackCtx * c) {
     if (c->g_token) cudaGraphExecDestroy(c->g_token);
     if (c->g_greedy) cudaGraphExecDestroy(c->g_greedy);
     cudaFree(c->d_out_tokens); cudaFree(c->d_counter);
-    for (float * p : { c->Y2, c->U, c->XC }) cudaFree(p);
+    for (float * p : { c->Y2, c->U, c->XC, c->keep, c->Xp, c->Ap, c->Yk, c->r_wt, c->r_sg }) cudaFree(p);
+    for (int32_t * p : { c->r_sel, c->r_slot, c->r_src, c->r_seg }) cudaFree(p);
     for (float * p : { c->X, c->Hn, c->Y, c->P, c->A, c->QK, c->OL, c->CV, c->BG, c->O, c->rec, c->d_logits }) cudaFree(p);
     for (float * p : c->cache_allocs) cudaFree(p);
     cudaFree(c->att_scores); cudaFree(c->da_part); cudaFree(c->da_counter);
@@ -1086,11 +1505,20 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
         const bool par = m->block == BLOCK_PARALLEL;
         fl(&c->X, cap * m->E); fl(&c->Hn, cap * m->E * (par ? 2 : 1)); fl(&c->Y, cap * m->E);
         if (par) { fl(&c->Y2, cap * m->E); fl(&c->U, cap * m->E * 2); fl(&c->XC, cap * m->E * 2); }
+        else if (m->has_pair) fl(&c->Y2, cap * m->E);
+        if (m->depth_avg) fl(&c->keep, (m->layers.size() + 1) * cap * m->E);
+        size_t moe_rows = 0;
+        if (m->max_slots > 0) {
+            moe_rows = cap * (size_t) m->max_slots;
+            fl(&c->Xp, moe_rows * m->E); fl(&c->Ap, moe_rows * m->max_eff); fl(&c->Yk, moe_rows * m->E);
+            fl(&c->r_wt, moe_rows); fl(&c->r_sg, cap);
+            fl((float **) &c->r_sel, moe_rows); fl((float **) &c->r_slot, moe_rows); fl((float **) &c->r_src, moe_rows); fl((float **) &c->r_seg, (size_t) m->max_exp + 1);
+        }
         fl(&c->P, cap * m->maxP); fl(&c->A, cap * m->maxA); fl(&c->QK, cap_t * m->maxQK); fl(&c->OL, cap_t * m->maxOL);
         fl(&c->CV, cap * m->maxCV); fl(&c->BG, cap * m->maxBG); fl(&c->O, cap * m->maxA);
         fl(&c->rec, m->rec_floats);
         if (m->dtype == STACK_BF16) {
-            c->xb_elems = cap * (size_t) std::max({ 2 * m->E, m->maxA, m->maxOL, m->maxP });
+            c->xb_elems = std::max(cap * (size_t) std::max({ 2 * m->E, m->maxA, m->maxOL, m->maxP }), moe_rows * (size_t) std::max(m->E, m->max_eff));
             SCU(cudaMalloc(&c->xb, c->xb_elems * 2));
         }
         SCU(cudaMalloc(&c->d_err, 4)); SCU(cudaMemsetAsync(c->d_err, 0, 4, c->st));
@@ -1100,9 +1528,18 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
         SCU(cudaGetDeviceProperties(&prop, m->device));
         c->sm_count = prop.multiProcessorCount;
         size_t smem = 0, part = 0, ml = 0, da_part = 0, da_cnt = 0;
+        struct Cached { const LayerSpec * L; int index; };
+        std::vector<Cached> cached;           // every attention cache of every run (a pair's branches each have their own)
         for (const RunSpec & R : m->runs) {
             const LayerSpec & L = m->layers[(size_t) R.layer];
             if (R.cache_index < 0) continue;
+            if (L.kind != MIX_PAIR) { cached.push_back({ &L, R.cache_index }); continue; }
+            int at = R.cache_index;
+            for (const LayerSpec & B : L.parts) if (B.cache_row) cached.push_back({ &B, at++ });
+        }
+        for (const Cached & cd : cached) {
+            const LayerSpec & L = *cd.L;
+            const struct { int cache_index; } R{ cd.index };
             {   // [ window - 1 zero rows | n_ctx positions | one tile of slack ]: a tile's key range may start before position 0 and end past the portion
                 const size_t front = (size_t) std::max(L.window, 1), rows = front + (size_t) n_ctx + 2 * ATT_TQ;
                 float * base = nullptr;
@@ -1117,6 +1554,11 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
             if (L.kind == MIX_DIFFATTN) {
                 const size_t mgw = 4 + 64 * (size_t) (L.V <= 32 ? 1 : L.V <= 64 ? 2 : L.V <= 128 ? 4 : 8);
                 da_part = std::max(da_part, (size_t) 8 * L.H * DIFF_MAX_SPLIT * mgw);
+                da_cnt = std::max(da_cnt, (size_t) 8 * L.H);
+                continue;
+            }
+            if (L.kind == MIX_SIGATTN) {
+                da_part = std::max(da_part, (size_t) 8 * L.H * SIG_MAX_SPLIT * 32 * (size_t) sig_vpl(L));
                 da_cnt = std::max(da_cnt, (size_t) 8 * L.H);
                 continue;
             }

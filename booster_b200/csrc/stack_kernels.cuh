@@ -150,10 +150,17 @@ struct LinArgs {
                         // w_kn = 0 and ldw > 0: W is [N][K] with row stride ldw (keys inside wider cached rows)
     int nz2 = 1;        // k_gemm_simt only: blockIdx.z = z1 * nz2 + z2, a second batch level with the strides below
     long long sX2 = 0, sW2 = 0, sY2 = 0;
+    float up_shift = 1.0f;                  // the gated unit's (u + up_shift)
+    // tile kernels: batch entry z works on rows seg[z] .. seg[z + 1] - 1 of X and Y (rows sorted by the matrix they meet: a routed
+    // mixture's experts); T is then only the most rows an entry can have
+    const int32_t * seg = nullptr;
+    // k_gemv: entry z meets matrix w_index[z] of the batch and reads the rows of entry z / x_share
+    const int32_t * w_index = nullptr;
+    int x_share = 1;
 };
-__device__ __forceinline__ float clamped_glu(float gate, float up, float limit, float alpha) {
-    const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
-    return g * sigmoidf_(alpha * g) * (u + 1.0f);
+__device__ __forceinline__ float clamped_glu(float gate, float up, float limit, float alpha, float shift) {
+    const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);      // limit = +inf: no clamp
+    return g * sigmoidf_(alpha * g) * (u + shift);
 }
 
 constexpr int GEMV_MAX_T = 4;
@@ -163,8 +170,8 @@ __global__ void __launch_bounds__(256) k_gemv(const LinArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int n = (blockIdx.x * (blockDim.x >> 5) + warp) * RPW;      // RPW = 2: a (gate, up) pair per warp
     if (n >= a.N) return;
-    const WT * w = reinterpret_cast<const WT *>(a.W) + (size_t) blockIdx.z * a.sW + (size_t) n * a.K;
-    const float * x = a.X + (size_t) blockIdx.z * a.sX;
+    const WT * w = reinterpret_cast<const WT *>(a.W) + (size_t) (a.w_index ? a.w_index[blockIdx.z] : blockIdx.z) * a.sW + (size_t) n * a.K;
+    const float * x = a.X + (size_t) (blockIdx.z / a.x_share) * a.sX;
     float acc[RPW][GEMV_MAX_T];
 #pragma unroll
     for (int r = 0; r < RPW; r++)
@@ -233,7 +240,7 @@ __global__ void __launch_bounds__(256) k_gemv(const LinArgs a) {
             for (int r = 0; r < RPW; r++) s[r] = warp_sum(acc[r][t]) + (a.bias ? a.bias[n + r] : 0.f);
             if (lane == 0) {
                 float * y = a.Y + (size_t) blockIdx.z * a.sY + (size_t) t * a.ldy;
-                if constexpr (RPW == 2) y[n >> 1] = clamped_glu(s[0], s[1], a.limit, a.alpha);
+                if constexpr (RPW == 2) y[n >> 1] = clamped_glu(s[0], s[1], a.limit, a.alpha, a.up_shift);
                 else y[n] = s[0];
             }
         }
@@ -249,7 +256,9 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const LinArgs a) {
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
     const int z1 = blockIdx.z / a.nz2, z2 = blockIdx.z - z1 * a.nz2;
-    const float * X = a.X + (size_t) z1 * a.sX + (size_t) z2 * a.sX2;
+    const int r0 = a.seg ? a.seg[blockIdx.z] : 0, T = a.seg ? a.seg[blockIdx.z + 1] - r0 : a.T;
+    if (m0 >= T) return;
+    const float * X = a.seg ? a.X + (size_t) r0 * a.ldx : a.X + (size_t) z1 * a.sX + (size_t) z2 * a.sX2;
     const WT * W = reinterpret_cast<const WT *>(a.W) + (size_t) z1 * a.sW + (size_t) z2 * a.sW2;
     const int lr = tid >> 2, lk = (tid & 3) * 4;          // this thread stages 4 consecutive k of row lr
     float acc[4][4];
@@ -261,7 +270,7 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const LinArgs a) {
         {
             const int m = m0 + lr;
             float v[4] = { 0.f, 0.f, 0.f, 0.f };
-            if (m < a.T) {
+            if (m < T) {
                 const float * p = X + (size_t) m * a.ldx + k0 + lk;
                 if (a.vec && k0 + lk + 3 < a.K) { const float4 f = *reinterpret_cast<const float4 *>(p); v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w; }
                 else for (int i = 0; i < 4; i++) if (k0 + lk + i < a.K) v[i] = p[i];
@@ -299,16 +308,16 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const LinArgs a) {
         }
         __syncthreads();
     }
-    float * Y = a.Y + (size_t) z1 * a.sY + (size_t) z2 * a.sY2;
+    float * Y = a.seg ? a.Y + (size_t) r0 * a.ldy : a.Y + (size_t) z1 * a.sY + (size_t) z2 * a.sY2;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int m = m0 + ty * 4 + i;
-        if (m >= a.T) continue;
+        if (m >= T) continue;
         if (a.glu) {
 #pragma unroll
             for (int j = 0; j < 4; j += 2) {
                 const int n = n0 + tx * 4 + j;
-                if (n + 1 < a.N) Y[(size_t) m * a.ldy + (n >> 1)] = clamped_glu(acc[i][j] + (a.bias ? a.bias[n] : 0.f), acc[i][j + 1] + (a.bias ? a.bias[n + 1] : 0.f), a.limit, a.alpha);
+                if (n + 1 < a.N) Y[(size_t) m * a.ldy + (n >> 1)] = clamped_glu(acc[i][j] + (a.bias ? a.bias[n] : 0.f), acc[i][j + 1] + (a.bias ? a.bias[n + 1] : 0.f), a.limit, a.alpha, a.up_shift);
             }
             continue;
         }
@@ -342,7 +351,9 @@ __global__ void __launch_bounds__(256) k_gemm_bf16_mma(const LinArgs a) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;
     const int m0 = blockIdx.y * MM_BM, n0 = blockIdx.x * MM_BN;
-    const float * X = a.X + (size_t) blockIdx.z * a.sX;
+    const int r0 = a.seg ? a.seg[blockIdx.z] : 0, T = a.seg ? a.seg[blockIdx.z + 1] - r0 : a.T;
+    if (m0 >= T) return;
+    const float * X = a.seg ? a.X + (size_t) r0 * a.ldx : a.X + (size_t) blockIdx.z * a.sX;
     const __nv_bfloat16 * W = reinterpret_cast<const __nv_bfloat16 *>(a.W) + (size_t) blockIdx.z * a.sW;
     // staging: 128 rows x 32 k per operand; thread -> (row = tid / 2 [+ 0], 16 consecutive k starting at (tid & 1) * 16)
     const int sr = tid >> 1, sk = (tid & 1) * 16;
@@ -352,7 +363,7 @@ __global__ void __launch_bounds__(256) k_gemm_bf16_mma(const LinArgs a) {
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int k = k0 + sk + 4 * i;
-            xa[i] = (m < a.T && k < a.K) ? *reinterpret_cast<const float4 *>(X + (size_t) m * a.ldx + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+            xa[i] = (m < T && k < a.K) ? *reinterpret_cast<const float4 *>(X + (size_t) m * a.ldx + k) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int i = 0; i < 2; i++) {
@@ -400,7 +411,7 @@ __global__ void __launch_bounds__(256) k_gemm_bf16_mma(const LinArgs a) {
         if (kt + 1 < nk) stash(buf ^ 1);
         __syncthreads();
     }
-    float * Y = a.Y + (size_t) blockIdx.z * a.sY;
+    float * Y = a.seg ? a.Y + (size_t) r0 * a.ldy : a.Y + (size_t) blockIdx.z * a.sY;
 #pragma unroll
     for (int i = 0; i < 4; i++)
 #pragma unroll
@@ -410,9 +421,9 @@ __global__ void __launch_bounds__(256) k_gemm_bf16_mma(const LinArgs a) {
                 const int m = m0 + wm + 16 * i + (lane >> 2) + (e >> 1) * 8;
                 const int n = n0 + wn + 8 * j + (lane & 3) * 2 + (e & 1);
                 if (a.glu) {            // this thread holds the (gate, up) pair of unit n / 2 in elements e, e + 1
-                    if (!(e & 1) && m < a.T && n + 1 < a.N)
-                        Y[(size_t) m * a.ldy + (n >> 1)] = clamped_glu(acc[i][j][e] + (a.bias ? a.bias[n] : 0.f), acc[i][j][e + 1] + (a.bias ? a.bias[n + 1] : 0.f), a.limit, a.alpha);
-                } else if (m < a.T && n < a.N) Y[(size_t) m * a.ldy + n] = acc[i][j][e] + (a.bias ? a.bias[n] : 0.f);
+                    if (!(e & 1) && m < T && n + 1 < a.N)
+                        Y[(size_t) m * a.ldy + (n >> 1)] = clamped_glu(acc[i][j][e] + (a.bias ? a.bias[n] : 0.f), acc[i][j][e + 1] + (a.bias ? a.bias[n + 1] : 0.f), a.limit, a.alpha, a.up_shift);
+                } else if (m < T && n < a.N) Y[(size_t) m * a.ldy + n] = acc[i][j][e] + (a.bias ? a.bias[n] : 0.f);
             }
 }
 
@@ -455,7 +466,9 @@ __global__ void __launch_bounds__(256, 1) k_gemm_bf16_umma(const LinArgs a, cons
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t smem0 = (smem_addr(um_raw) + 1023u) & ~1023u;
     const int m0 = blockIdx.y * UM_BM, n0 = blockIdx.x * UM_BN;
-    const __nv_bfloat16 * X = Xb + (size_t) blockIdx.z * sXb;
+    const int r0 = a.seg ? a.seg[blockIdx.z] : 0, T = a.seg ? a.seg[blockIdx.z + 1] - r0 : a.T;
+    if (m0 >= T) return;                      // the whole block, before anything is allocated
+    const __nv_bfloat16 * X = a.seg ? Xb + (size_t) r0 * a.K : Xb + (size_t) blockIdx.z * sXb;
     const __nv_bfloat16 * W = reinterpret_cast<const __nv_bfloat16 *>(a.W) + (size_t) blockIdx.z * a.sW;
     volatile int * failed = &failed_s;
     if (tid == 0) {
@@ -484,7 +497,7 @@ __global__ void __launch_bounds__(256, 1) k_gemm_bf16_umma(const LinArgs a, cons
             const uint32_t off = (uint32_t) rg * 1024u + (uint32_t) kc * 128u + (uint32_t) r_in * 16u;
             if (i < 4) {
                 const int m = m0 + rg * 8 + r_in;
-                const bool ok = m < a.T && k < a.K;
+                const bool ok = m < T && k < a.K;
                 cp_async16(sa + off, ok ? (const void *) (X + (size_t) m * a.K + k) : (const void *) X, ok ? 16u : 0u);
             } else {
                 const int n = n0 + rg * 8 + r_in;
@@ -533,7 +546,7 @@ __global__ void __launch_bounds__(256, 1) k_gemm_bf16_umma(const LinArgs a, cons
     if (ok) {
         const int m = m0 + 32 * (warp & 3) + lane, cbase = (warp >> 2) * (UM_BN / 2);
         const uint32_t taddr = tmem + ((uint32_t) (32 * (warp & 3)) << 16) + (uint32_t) cbase;
-        float * Y = a.Y + (size_t) blockIdx.z * a.sY + (size_t) m * a.ldy;
+        float * Y = (a.seg ? a.Y + (size_t) r0 * a.ldy : a.Y + (size_t) blockIdx.z * a.sY) + (size_t) m * a.ldy;
 #pragma unroll 1
         for (int c = 0; c < UM_BN / 2; c += 16) {
             float v[16];
@@ -544,7 +557,7 @@ __global__ void __launch_bounds__(256, 1) k_gemm_bf16_umma(const LinArgs a, cons
                 v[4 * j] = __uint_as_float(r0); v[4 * j + 1] = __uint_as_float(r1); v[4 * j + 2] = __uint_as_float(r2); v[4 * j + 3] = __uint_as_float(r3);
             }
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (m < a.T) {
+            if (m < T) {
                 const int nb = n0 + cbase + c;
                 if (!a.glu && nb + 15 < a.N && (a.ldy & 3) == 0 && ((uintptr_t) (Y + nb) & 15) == 0) {       // whole 16-byte stores
 #pragma unroll
@@ -559,7 +572,7 @@ __global__ void __launch_bounds__(256, 1) k_gemm_bf16_umma(const LinArgs a, cons
                 for (int j = 0; j < 16; j += 2) {
                     const int n = n0 + cbase + c + j;
                     if (a.glu) {
-                        if (n + 1 < a.N) Y[n >> 1] = clamped_glu(v[j] + (a.bias ? a.bias[n] : 0.f), v[j + 1] + (a.bias ? a.bias[n + 1] : 0.f), a.limit, a.alpha);
+                        if (n + 1 < a.N) Y[n >> 1] = clamped_glu(v[j] + (a.bias ? a.bias[n] : 0.f), v[j + 1] + (a.bias ? a.bias[n + 1] : 0.f), a.limit, a.alpha, a.up_shift);
                     } else {
                         if (n < a.N) Y[n] = v[j] + (a.bias ? a.bias[n] : 0.f);
                         if (n + 1 < a.N) Y[n + 1] = v[j + 1] + (a.bias ? a.bias[n + 1] : 0.f);
@@ -1104,8 +1117,8 @@ __global__ void k_delta_out(const float * __restrict__ O, const float * __restri
         for (int i = lane; i < V; i += 32) ss = fmaf(o[i], o[i], ss);
         ss = warp_sum(ss);
         const float r = 1.0f / sqrtf(ss / (float) V + eps);
-        const float * nw = normw + (size_t) h * w_stride;
-        for (int i = lane; i < V; i += 32) A[(size_t) t * H * V + (size_t) h * V + i] = o[i] * r * nw[i] * (gate_sigmoid ? sigmoidf_(gp[i]) : siluf_(gp[i]));
+        const float * nw = normw ? normw + (size_t) h * w_stride : nullptr;      // nullptr: no weight
+        for (int i = lane; i < V; i += 32) A[(size_t) t * H * V + (size_t) h * V + i] = o[i] * r * (nw ? nw[i] : 1.0f) * (gate_sigmoid ? sigmoidf_(gp[i]) : siluf_(gp[i]));
     }
 }
 

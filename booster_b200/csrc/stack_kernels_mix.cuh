@@ -1,0 +1,451 @@
+// stack_kernels_mix.cuh — more CUDA kernels (sm_100a) of the layer-stack models, beside stack_kernels.cuh: an element-wise
+// norm without statistics (dynamic tanh), the sub-layer join with a depth-weighted average over the outputs of all earlier
+// layers, retention (matrix state with a constant decay per head), sigmoid attention with a linear distance penalty over
+// grouped key/value heads, and the routed mixture of gated units (router with group-limited choice, expert-sorted rows for
+// the segmented products of prompt portions, indexed mat-vecs for single tokens).
+// Every size and constant is a kernel argument. Everything here is float32: norms, positions and angles, scores and
+// weights, the recurrent state, the router.
+#pragma once
+#include "stack_kernels.cuh"
+
+namespace b200 {
+namespace stk {
+
+// ---- dynamic tanh: y = tanh(alpha x) w + b, element by element (no mean, no variance) -----------------------------------------
+struct DytW { const float * w; const float * b; float alpha; };
+__device__ __forceinline__ float dytf_(float x, const DytW & n, int i) { return fmaf(tanhf(n.alpha * x), n.w[i], n.b[i]); }
+
+// embedding under that norm: X[t] = dyt_e(embed[token[t]]) (also kept as plane 0 of the depth history when given),
+// Hn[t] = dyt_1(X[t]) for the first layer
+template <typename WT>
+__global__ void k_embed_dyt(const WT * __restrict__ embed, const int32_t * __restrict__ tokens, int E, int n_vocab, DytW ne, DytW n1,
+                            float * __restrict__ X, float * __restrict__ keep0, float * __restrict__ Hn) {
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    tok = tok < 0 ? 0 : tok >= n_vocab ? n_vocab - 1 : tok;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+        const float v = dytf_(wf(embed, (size_t) tok * E + i), ne, i);
+        X[(size_t) t * E + i] = v;
+        if (keep0) keep0[(size_t) t * E + i] = v;
+        Hn[(size_t) t * E + i] = dytf_(v, n1, i);
+    }
+}
+// the head's input: Y[r] = dyt(X[rows[r]]) on the wanted rows
+__global__ void k_dyt_rows(const float * __restrict__ X, int ldx, const int32_t * __restrict__ rows, DytW n, int E, float * __restrict__ Y, int ldy) {
+    const int r = blockIdx.x, src = rows ? rows[r] : r;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) Y[(size_t) r * ldy + i] = dytf_(X[(size_t) src * ldx + i], n, i);
+}
+
+// ---- end of a sub-layer ---------------------------------------------------------------------------------------------------------
+// v = X[t] + y[t], where y is one of
+//   plain     Ya[t]
+//   pair      (rms(Ya[t]) wa + rms(Yb[t]) wb) / 2: two branches that read the same input, each over its root mean square across
+//             the row (eps inside the root) times a plain weight
+//   mixture   sum_k wt[t][k] Yk[slot(t, k)] (+ sg[t] Ysh[t]): the chosen experts' outputs, found through slot_of when the rows were
+//             sorted by expert (nullptr: slot t top + k), plus the gated shared unit
+// then, when the layer ends here and the design averages over depth: keep[n_keep - 1][t] = v and
+// v <- sum_(j < n_keep) coef[j] keep[j][t] (planes of `plane` floats; plane 0 is the embedding output); X[t] = v; and
+// Hn[t] = dyt(v) for the sub-layer that follows. grid (T, slices of JOIN_SLICE entries); a pair's two sums of squares are taken
+// by every slice's block over the whole row.
+constexpr int JOIN_SLICE = 1024;
+struct JoinArgs {
+    float * X; int E;
+    const float * Ya; const float * Yb; const float * wa; const float * wb; float eps;      // Yb != nullptr: pair
+    const float * Yk; const float * wt; const int32_t * slot_of; int top; const float * Ysh; const float * sg;   // Yk != nullptr: mixture
+    float * keep; long long plane; const float * coef; int n_keep;                          // keep != nullptr: depth average
+    const float * nw; const float * nb; float alpha; float * Hn;                            // nw != nullptr: the next norm
+};
+__global__ void __launch_bounds__(256) k_join(const JoinArgs a) {
+    __shared__ float red[2][8];
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const size_t row = (size_t) t * a.E;
+    float ra = 1.f, rb = 1.f;
+    if (a.Yb) {
+        float sa = 0.f, sb = 0.f;
+        for (int i = tid; i < a.E; i += 256) { const float u = a.Ya[row + i], v = a.Yb[row + i]; sa = fmaf(u, u, sa); sb = fmaf(v, v, sb); }
+        sa = warp_sum(sa); sb = warp_sum(sb);
+        if ((tid & 31) == 0) { red[0][tid >> 5] = sa; red[1][tid >> 5] = sb; }
+        __syncthreads();
+        float ta = 0.f, tb = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) { ta += red[0][w]; tb += red[1][w]; }
+        ra = 1.0f / sqrtf(ta / (float) a.E + a.eps); rb = 1.0f / sqrtf(tb / (float) a.E + a.eps);
+    }
+    const int i1 = min(a.E, (int) (blockIdx.y + 1) * JOIN_SLICE);
+    for (int i = blockIdx.y * JOIN_SLICE + tid; i < i1; i += 256) {
+        float y;
+        if (a.Yb) y = 0.5f * fmaf(a.Ya[row + i] * ra, a.wa[i], a.Yb[row + i] * rb * a.wb[i]);
+        else if (a.Yk) {
+            y = 0.f;
+            for (int k = 0; k < a.top; k++) {
+                const int s = t * a.top + k;
+                y = fmaf(a.wt[s], a.Yk[(size_t) (a.slot_of ? a.slot_of[s] : s) * a.E + i], y);
+            }
+            if (a.Ysh) y = fmaf(a.sg[t], a.Ysh[row + i], y);
+        } else y = a.Ya[row + i];
+        float v = a.X[row + i] + y;
+        if (a.keep) {
+            a.keep[(size_t) (a.n_keep - 1) * a.plane + row + i] = v;
+            float z = a.coef[a.n_keep - 1] * v;
+            for (int j = a.n_keep - 2; j >= 0; j--) z = fmaf(a.coef[j], a.keep[(size_t) j * a.plane + row + i], z);
+            v = z;
+        }
+        a.X[row + i] = v;
+        if (a.nw) a.Hn[row + i] = fmaf(tanhf(a.alpha * v), a.nw[i], a.nb[i]);
+    }
+}
+
+// ---- retention: S <- decay_h S + k v^T, o = S^T q per head; no soft-max, no denominator --------------------------------------------
+// P[t] = [ q: H x D | k: H x D | v: H x V | output-gate pre-activation: H x V ].
+// Step 1, per token, in place: the first rope.dims entries of every q and k head are rotated by the token's position
+// ('rotate half' pairs), then k is scaled by k_scale (D^(-1/2)). One block per token, a warp per head.
+__global__ void k_retention_prep(float * __restrict__ P, int ldp, int q_off, int k_off, int H, int D, RopeArgs rope, float k_scale, const StepState * __restrict__ st) {
+    const int t = blockIdx.x, pos = st->pos0 + t;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5, half = rope.dims / 2;
+    for (int v = warp; v < 2 * H; v += nw) {
+        const bool is_k = v >= H;
+        float * x = P + (size_t) t * ldp + (is_k ? k_off + (size_t) (v - H) * D : q_off + (size_t) v * D);
+        const float f = is_k ? k_scale : 1.0f;
+        for (int i = lane; i < D; i += 32) {
+            if (i < half) { float a, b; rope_pair(rope, pos, i, x[i], x[i + half], a, b); x[i] = a * f; x[i + half] = b * f; }
+            else if (i >= rope.dims && is_k) x[i] *= f;
+        }
+    }
+}
+// Step 2, the recurrence. S is [D][V] per head in float32 and stays in registers for the whole portion; four neighbouring lanes
+// share one column of S, each holding a quarter of its rows, and close the read-out with two shuffles. q and k of a few tokens
+// arrive in shared memory by asynchronous copies while the tokens before them are walked (two buffers); each quarter of the rows
+// is padded apart so that the four lanes' reads fall into different banks. A head's columns are spread over gridDim.y blocks.
+template <int DMAX>
+__global__ void __launch_bounds__(512) k_retention_scan(const float * __restrict__ P, int ldp, int q_off, int k_off, int v_off, const float * __restrict__ decay,
+                                                        int T, int H, int D, int V, float * __restrict__ S, float * __restrict__ O) {
+    constexpr int TT = DMAX > 128 ? 4 : 8, DR = DMAX / GD_RG, ROW = GD_RG * (DR + GD_PAD);
+    __shared__ __align__(16) float qs[2][TT][ROW], ks[2][TT][ROW], vs[2][TT][128];
+    const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, rg = lane & 3, ncols = blockDim.x / GD_RG;
+    const int cl = (tid >> 5) * 8 + (lane >> 2), col = blockIdx.y * ncols + cl;
+    const bool live = col < V;
+    const float g = decay[h];
+    const auto stage = [&](int t0, int buf) {
+        const int nt = min(TT, T - t0);
+        for (int i = tid; i < nt * DMAX; i += blockDim.x) {
+            const int tt = i / DMAX, d = i % DMAX, at = (d / DR) * (DR + GD_PAD) + d % DR;
+            const bool in = d < D;
+            const float * p = P + (size_t) (t0 + tt) * ldp + (size_t) h * D + (in ? d : 0);
+            cp_async4(&qs[buf][tt][at], p + q_off, in);
+            cp_async4(&ks[buf][tt][at], p + k_off, in);
+        }
+        for (int i = tid; i < nt * ncols; i += blockDim.x) {
+            const int tt = i / ncols, c = i % ncols;
+            const bool in = blockIdx.y * ncols + c < V;
+            cp_async4(&vs[buf][tt][c], P + (size_t) (t0 + tt) * ldp + v_off + (size_t) h * V + (in ? blockIdx.y * ncols + c : 0), in);
+        }
+    };
+    stage(0, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    float s[DR];
+    float * Sh = S + (size_t) h * D * V;
+#pragma unroll
+    for (int i = 0; i < DR; i++) { const int d = rg * DR + i; s[i] = (live && d < D) ? Sh[(size_t) d * V + col] : 0.f; }
+    const int base = rg * (DR + GD_PAD);
+    for (int t0 = 0, buf = 0; t0 < T; t0 += TT, buf ^= 1) {
+        const int nt = min(TT, T - t0);
+        if (t0 + TT < T) stage(t0 + TT, buf ^ 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();
+        for (int tt = 0; tt < nt; tt++) {
+            const float v = vs[buf][tt][cl];
+            float op[4] = { 0.f, 0.f, 0.f, 0.f };
+#pragma unroll
+            for (int i = 0; i < DR; i++) {
+                s[i] = fmaf(g, s[i], ks[buf][tt][base + i] * v);
+                op[i & 3] = fmaf(s[i], qs[buf][tt][base + i], op[i & 3]);
+            }
+            float o = (op[0] + op[1]) + (op[2] + op[3]);
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            if (rg == 0 && live) O[(size_t) (t0 + tt) * H * V + (size_t) h * V + col] = o;
+        }
+        __syncthreads();
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < DR; i++) { const int d = rg * DR + i; if (d < D) Sh[(size_t) d * V + col] = s[i]; }
+    }
+}
+
+// ---- sigmoid attention over grouped key/value heads -------------------------------------------------------------------------------
+// P[t] = [ q: H x D | k: G x D | v: G x V ]. Query head h reads key/value head h / (H / G); position p sees every j <= p.
+// The weight of key j for head h is sigmoid((q . k_j) scale - slope[h] (p - j) + pb[h]); weights are not normalised over keys.
+// Step 1, per token: q and k are each divided by the root mean square of their WHOLE projection (all heads at once, eps inside
+// the root) and multiplied by plain weights; q is also multiplied by the position's temperature
+// 1 + coef ln(floor((p + 1) / every) + 1); every value head is divided by its own root mean square (no weight). Queries go to
+// Q[t] (H x D), keys and values to the cache row of the position: [ k: G x D | v: G x V ]. One block per token.
+__global__ void __launch_bounds__(256) k_sigattn_prep(const float * __restrict__ P, int ldp, int H, int G, int D, int V, const float * __restrict__ qw, const float * __restrict__ kw,
+                                                      float eps, float t_coef, int t_every, const StepState * __restrict__ st, float * __restrict__ Q, float * __restrict__ cache) {
+    __shared__ float red[2][8];
+    const int t = blockIdx.x, pos = st->pos0 + t, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nq = H * D, nk = G * D;
+    const float * q = P + (size_t) t * ldp, * k = q + nq, * v = k + nk;
+    float sq = 0.f, sk = 0.f;
+    for (int i = tid; i < nq; i += 256) sq = fmaf(q[i], q[i], sq);
+    for (int i = tid; i < nk; i += 256) sk = fmaf(k[i], k[i], sk);
+    sq = warp_sum(sq); sk = warp_sum(sk);
+    if (lane == 0) { red[0][warp] = sq; red[1][warp] = sk; }
+    __syncthreads();
+    float tq = 0.f, tk = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) { tq += red[0][w]; tk += red[1][w]; }
+    const float temp = t_every > 0 ? 1.0f + t_coef * logf((float) ((pos + 1) / t_every) + 1.0f) : 1.0f;
+    const float rq = temp / sqrtf(tq / (float) nq + eps), rk = 1.0f / sqrtf(tk / (float) nk + eps);
+    float * row = cache + (size_t) pos * (nk + G * V);
+    for (int i = tid; i < nq; i += 256) Q[(size_t) t * nq + i] = q[i] * rq * qw[i];
+    for (int i = tid; i < nk; i += 256) row[i] = k[i] * rk * kw[i];
+    for (int g = warp; g < G; g += 8) {
+        const float * x = v + (size_t) g * V;
+        float ss = 0.f;
+        for (int i = lane; i < V; i += 32) ss = fmaf(x[i], x[i], ss);
+        ss = warp_sum(ss);
+        const float r = 1.0f / sqrtf(ss / (float) V + eps);
+        for (int i = lane; i < V; i += 32) row[nk + (size_t) g * V + i] = x[i] * r;
+    }
+}
+// Step 2 for steps of few tokens: a block takes TQ consecutive tokens of one head; the 8 / TQ warps of a query and the nsplit blocks
+// of blockIdx.z walk its keys in alternating chunks of 32 (a lane per key for the score, a lane per 32nd value channel for the
+// weighted sum). Without a soft-max the partial sums simply add: the query's warps through shared memory, the blocks through
+// `part`, summed in a fixed order by the block that finishes last (an atomic counter, no waiting).
+struct SigAttnArgs {
+    const float * Q; int ldq;
+    const float * cache; int ldc;
+    const StepState * st;
+    float * A;                  // [T][H x V]
+    const float * slope; const float * pb;      // [H] each
+    int T, H, G, D, V;
+    float scale;
+    int TQ, vec, nsplit;
+    float * part;               // [T][H][nsplit][32 VPL]
+    int * counter;              // [T][H]
+};
+template <int VPL>
+__global__ void __launch_bounds__(256) k_sig_attn(const SigAttnArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int WPQ = 8 / a.TQ, qi = warp / WPQ, wq = warp % WPQ;
+    const int h = blockIdx.y, g = h / (a.H / a.G), t0 = blockIdx.x * a.TQ, t = t0 + qi;
+    float * qs = sm;                                        // [TQ][D]
+    float * mg = sm + (size_t) a.TQ * a.D;                  // [8 warps][32 VPL]
+    constexpr int MGW = 32 * VPL;
+    for (int i = tid; i < a.TQ * a.D; i += 256) {
+        const int q = i / a.D, e = i - q * a.D;
+        qs[i] = t0 + q < a.T ? a.Q[(size_t) (t0 + q) * a.ldq + (size_t) h * a.D + e] : 0.f;
+    }
+    __syncthreads();
+    float acc[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; i++) acc[i] = 0.f;
+    if (t < a.T) {
+        const int p = a.st->pos0 + t;
+        const int nchunk = (p + 1 + 31) / 32;
+        const float * q1 = qs + (size_t) qi * a.D;
+        const float slope = a.slope[h], pb = a.pb[h];
+        const size_t koff = (size_t) g * a.D, voff = (size_t) a.G * a.D + (size_t) g * a.V;
+        for (int c = blockIdx.z * WPQ + wq; c < nchunk; c += WPQ * a.nsplit) {
+            const int jb = c * 32, j = jb + lane, cnt = min(32, p - jb + 1);
+            float w = 0.f;
+            if (lane < cnt) {
+                const float * k1 = a.cache + (size_t) j * a.ldc + koff;
+                float x0 = 0.f, x1 = 0.f;
+                if (a.vec) {
+#pragma unroll 8
+                    for (int e = 0; e < a.D; e += 4) {
+                        const float4 ka = __ldg(reinterpret_cast<const float4 *>(k1 + e));
+                        const float4 qa = *reinterpret_cast<const float4 *>(q1 + e);
+                        x0 = fmaf(qa.x, ka.x, x0); x1 = fmaf(qa.y, ka.y, x1); x0 = fmaf(qa.z, ka.z, x0); x1 = fmaf(qa.w, ka.w, x1);
+                    }
+                } else {
+                    for (int e = 0; e < a.D; e++) x0 = fmaf(q1[e], k1[e], x0);
+                }
+                w = sigmoidf_(fmaf(x0 + x1, a.scale, pb - slope * (float) (p - j)));
+            }
+            const float * vrow = a.cache + (size_t) jb * a.ldc + voff;
+#pragma unroll 4
+            for (int kk = 0; kk < cnt; kk++) {
+                const float wk = __shfl_sync(0xffffffffu, w, kk);
+#pragma unroll
+                for (int i = 0; i < VPL; i++) {
+                    const int vi = lane + 32 * i;
+                    const float v = vi < a.V ? __ldg(vrow + (size_t) kk * a.ldc + vi) : 0.f;
+                    acc[i] = fmaf(wk, v, acc[i]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < VPL; i++) mg[(size_t) warp * MGW + lane + 32 * i] = acc[i];
+    __syncthreads();
+    if (wq != 0 || t >= a.T) return;
+#pragma unroll
+    for (int i = 0; i < VPL; i++) acc[i] = 0.f;
+    for (int w = 0; w < WPQ; w++)
+#pragma unroll
+        for (int i = 0; i < VPL; i++) acc[i] += mg[(size_t) (warp + w) * MGW + lane + 32 * i];
+    if (a.nsplit > 1) {
+        const size_t th = (size_t) t * a.H + h;
+        float * o = a.part + (th * a.nsplit + blockIdx.z) * MGW;
+#pragma unroll
+        for (int i = 0; i < VPL; i++) o[lane + 32 * i] = acc[i];
+        __threadfence();
+        int done = 0;
+        if (lane == 0) done = atomicAdd(a.counter + th, 1);
+        done = __shfl_sync(0xffffffffu, done, 0);
+        if (done != a.nsplit - 1) return;
+        __threadfence();
+        if (lane == 0) a.counter[th] = 0;
+        const float * ps = a.part + th * a.nsplit * MGW;
+#pragma unroll
+        for (int i = 0; i < VPL; i++) acc[i] = 0.f;
+        for (int z = 0; z < a.nsplit; z++)
+#pragma unroll
+            for (int i = 0; i < VPL; i++) acc[i] += __ldcg(ps + (size_t) z * MGW + lane + 32 * i);
+    }
+#pragma unroll
+    for (int i = 0; i < VPL; i++) if (lane + 32 * i < a.V) a.A[(size_t) t * a.H * a.V + (size_t) h * a.V + lane + 32 * i] = acc[i];
+}
+// Prompt portions run the same attention as two float32 products around an element-wise pass, like the other attentions of the
+// family: per tile of TQ tokens and key/value head g, S = Q_g K_g^T (rows: the tile's tokens x the R = H / G query heads of the
+// group), k_sig_weight_rows turns scores into weights, then O = W V_g.
+// queries [T][H][D] -> Qr[g][Tpad][R][D] (rows past T are zero)
+__global__ void k_group_q_layout(const float * __restrict__ Q, int ldq, int T, int Tpad, int H, int G, int D, float * __restrict__ Qr) {
+    const int t = blockIdx.x, R = H / G, nq = H * D;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+        const int h = i / D, d = i - h * D, g = h / R, hq = h - g * R;
+        Qr[(((size_t) g * Tpad + t) * R + hq) * D + d] = t < T ? Q[(size_t) t * ldq + i] : 0.f;
+    }
+}
+// S holds [g][n_rows = ng TQ R][nk] for a group of ng tiles starting at tile0; column n is key n (no window: the products
+// start at position 0). One warp per row.
+__global__ void k_sig_weight_rows(float * __restrict__ S, int n_rows, int G, int R, int TQ, int nk, const StepState * __restrict__ st, float scale,
+                                  const float * __restrict__ slope, const float * __restrict__ pb, int tile0, int T) {
+    const int lane = threadIdx.x & 31, id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (id >= n_rows * G) return;
+    const int g = id / n_rows, r = id - g * n_rows, h = g * R + r % R;
+    const int t = tile0 * TQ + r / R, p = st->pos0 + t;
+    float * s = S + (size_t) id * nk;
+    const float sl = slope[h], b = pb[h];
+    for (int n = lane; n < nk; n += 32) s[n] = (t < T && n <= p) ? sigmoidf_(fmaf(s[n], scale, b - sl * (float) (p - n))) : 0.f;
+}
+// Or[g][Tpad][R][V] -> A[t][h][V]
+__global__ void k_group_o_layout(const float * __restrict__ Or, int Tpad, int H, int G, int V, float * __restrict__ A) {
+    const int t = blockIdx.x, R = H / G;
+    for (int i = threadIdx.x; i < H * V; i += blockDim.x) {
+        const int h = i / V, d = i - h * V, g = h / R, hq = h - g * R;
+        A[(size_t) t * H * V + i] = Or[(((size_t) g * Tpad + t) * R + hq) * V + d];
+    }
+}
+
+// ---- routed mixture of gated units --------------------------------------------------------------------------------------------------
+// Router, per token, in float32: z = W_r h, s = softmax(z) over all n experts. The experts form n_groups equal groups of
+// neighbours; a group's score is its largest s; only experts of the `keep` best groups are eligible; the `top` eligible experts
+// with the largest s are chosen (lowest index first among equals) with weights s * scale, not renormalised.
+// sel[t][top], wt[t][top]; sg[t] = sigmoid(w_sg . h) is the shared unit's gate (w_sg == nullptr: no shared unit).
+// One block per token; dynamic shared memory: 2 n + n_groups floats.
+struct RouteArgs {
+    const float * Hn; int ld, E;
+    const float * Wr; const float * w_sg;
+    int n, top, n_groups, keep;
+    float scale;
+    int32_t * sel; float * wt; float * sg;
+};
+__global__ void __launch_bounds__(256) k_moe_route(const RouteArgs a) {
+    extern __shared__ float rsm[];
+    float * s = rsm, * elig = rsm + a.n, * gbest = rsm + 2 * a.n;
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const float * h = a.Hn + (size_t) t * a.ld;
+    for (int e = warp; e < a.n + (a.w_sg ? 1 : 0); e += nw) {
+        const float * w = e < a.n ? a.Wr + (size_t) e * a.E : a.w_sg;
+        float acc = 0.f;
+        for (int i = lane; i < a.E; i += 32) acc = fmaf(w[i], h[i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) { if (e < a.n) s[e] = acc; else a.sg[t] = sigmoidf_(acc); }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float mx = -INFINITY;
+    for (int e = lane; e < a.n; e += 32) mx = fmaxf(mx, s[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < a.n; e += 32) { const float v = expf(s[e] - mx); s[e] = v; sum += v; }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    __syncwarp();
+    const int per = a.n / a.n_groups;
+    for (int e = lane; e < a.n; e += 32) s[e] *= inv;
+    __syncwarp();
+    for (int g = lane; g < a.n_groups; g += 32) {
+        float b = -1.f;
+        for (int i = 0; i < per; i++) b = fmaxf(b, s[g * per + i]);
+        gbest[g] = b;
+    }
+    for (int e = lane; e < a.n; e += 32) elig[e] = -1.f;
+    __syncwarp();
+    // the best groups, one at a time; then the best eligible experts, one at a time (value, then lowest index)
+    for (int r = 0; r < a.keep; r++) {
+        float bv = -2.f; int bi = 0x7fffffff;
+        for (int g = lane; g < a.n_groups; g += 32) if (gbest[g] > bv) { bv = gbest[g]; bi = g; }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (bi != 0x7fffffff) {
+            for (int i = lane; i < per; i += 32) elig[bi * per + i] = s[bi * per + i];
+            if (lane == 0) gbest[bi] = -3.f;
+        }
+        __syncwarp();
+    }
+    for (int r = 0; r < a.top; r++) {
+        float bv = -0.5f; int bi = 0x7fffffff;
+        for (int e = lane; e < a.n; e += 32) if (elig[e] > bv) { bv = elig[e]; bi = e; }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (bi == 0x7fffffff) { bi = 0; bv = 0.f; }        // fewer eligible experts than `top` (refused at load): a slot of weight 0
+        if (lane == 0) { a.sel[t * a.top + r] = bi; a.wt[t * a.top + r] = bv * a.scale; elig[bi] = -1.f; }
+        __syncwarp();
+    }
+}
+// Prompt portions: the n_slots = T top (token, choice) slots sorted by expert, stably, so that every expert's rows are contiguous:
+// seg[e] .. seg[e + 1] - 1 are expert e's rows, slot_of[slot] the row a slot got, src_row[row] the token it reads. One block; a
+// thread per expert walks the slots in order.
+__global__ void k_moe_sort(const int32_t * __restrict__ sel, int n_slots, int top, int n, int32_t * __restrict__ seg, int32_t * __restrict__ slot_of, int32_t * __restrict__ src_row) {
+    extern __shared__ int cnt[];
+    for (int e = threadIdx.x; e < n; e += blockDim.x) {
+        int c = 0;
+        for (int s = 0; s < n_slots; s++) c += sel[s] == e;
+        cnt[e] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < n; e++) { seg[e] = at; at += cnt[e]; }
+        seg[n] = at;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n; e += blockDim.x) {
+        int at = seg[e];
+        for (int s = 0; s < n_slots; s++) if (sel[s] == e) { slot_of[s] = at; src_row[at] = s / top; at++; }
+    }
+}
+// Y[r] = X[src_row[r]]
+__global__ void k_gather_rows(const float * __restrict__ X, int ldx, const int32_t * __restrict__ src_row, int E, float * __restrict__ Y) {
+    const int r = blockIdx.x;
+    const float * x = X + (size_t) src_row[r] * ldx;
+    if ((E & 3) == 0 && (ldx & 3) == 0) {
+        for (int i = threadIdx.x * 4; i < E; i += blockDim.x * 4) *reinterpret_cast<float4 *>(Y + (size_t) r * E + i) = *reinterpret_cast<const float4 *>(x + i);
+    } else {
+        for (int i = threadIdx.x; i < E; i += blockDim.x) Y[(size_t) r * E + i] = x[i];
+    }
+}
+
+}  // namespace stk
+}  // namespace b200
