@@ -1,4 +1,4 @@
-"""Synthetic models of the layer-stack family (Matulorn and Dopilorn designs; config.json + model.safetensors) for benchmarks and smoke runs: random
+"""Synthetic models of the layer-stack family (Matulorn, Dopilorn and Tosevik designs; config.json + model.safetensors) for benchmarks and smoke runs: random
 bfloat16 weights of the right shapes, the counterpart of gguf_io.synth_llama for the GGUF path. Pure host code."""
 from __future__ import annotations
 
@@ -54,6 +54,70 @@ def dopilorn_config(width: int, n_layer: int, ff: int, heads: int, vocab: int = 
     return cfg
 
 
+def tosevik_config(width: int, n_layer: int, ff: int, heads: int, vocab: int = 32000, head_dim: int = 128, kv_heads: int = 0, experts: int = 16, top: int = 4,
+                   groups=(4, 2), pattern=("retention", "parallel")) -> dict:
+    """a Tosevik configuration whose layers resemble a real model's: mixers in `pattern` order, a routed mixture on every layer whose
+    chosen experts plus the shared unit are as wide together as a dense feed-forward of `ff` (top x 3 ff / 16 + ff / 4)"""
+    def ret(h, dim, vdim):
+        return {"heads": h, "dim": dim, "vdim": vdim, "rot": {"base": 1000000.0, "dims": dim // 2},
+                "decay": [1.0 - 2.0 ** (-5.0 - 3.0 * i / h) for i in range(h)]}
+    e_ff = max(8, ff * 3 // (4 * top) // 8 * 8)
+    layers = []
+    for i in range(n_layer):
+        kind = pattern[i % len(pattern)]
+        if kind == "retention":
+            mx = ret(heads, head_dim, head_dim)
+        else:
+            mx = {"left": {"heads": heads, "kv_heads": kv_heads or max(1, heads // 4), "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+                           "q_temp": {"coef": 0.1, "every": 1024}},
+                  "right": ret(heads, head_dim // 2, head_dim)}
+        mlp = {"kind": "moe", "expert": {"ff": e_ff}, "shared": {"ff": ff - top * e_ff},
+               "router": {"experts": experts, "top": top, "scale": 1.5, "groups": {"count": groups[0], "keep": groups[1]}}}
+        layers.append({"type": kind, "mixer": mx, "mlp": mlp})
+    return {"architecture": "Tosevik", "layers": layers, "norm": {"eps": 1e-6}, "vocab": vocab, "width": width}
+
+
+def tosevik_shapes(cfg: dict) -> Dict[str, List[int]]:
+    E, V = cfg["width"], cfg["vocab"]
+    t: Dict[str, List[int]] = {"embed": [V, E]}
+
+    def norm(name):
+        t[name] = [E]; t[name + ".b"] = [E]; t[name + ".alpha"] = []
+
+    def ret(p, mx):
+        H, D, Vd = mx["heads"], mx["dim"], mx["vdim"]
+        t.update({p + "q": [H * D, E], p + "k": [H * D, E], p + "v": [H * Vd, E], p + "g": [H * Vd, E], p + "o": [E, H * Vd]})
+    norm("embed.norm")
+    for i, L in enumerate(cfg["layers"]):
+        p, mx = f"l{i}.", L["mixer"]
+        norm(p + "norm1")
+        if L["type"] == "retention":
+            ret(p + "mix.", mx)
+        elif L["type"] == "parallel":
+            a = mx["left"]
+            H, G, D, Vd = a["heads"], a.get("kv_heads", a["heads"]), a["dim"], a["vdim"]
+            q = p + "mix.left."
+            t.update({q + "q": [H * D, E], q + "k": [G * D, E], q + "v": [G * Vd, E], q + "q.norm": [H * D], q + "k.norm": [G * D], q + "pb": [H], q + "o": [E, H * Vd],
+                      q + "out": [E], p + "mix.right.out": [E]})
+            ret(p + "mix.right.", mx["right"])
+        else:
+            raise ValueError(L["type"])
+        m = L.get("mlp")
+        if m:
+            norm(p + "norm2")
+            units = [(f"e{e}.", m["expert"]["ff"]) for e in range(m["router"]["experts"])]
+            if m.get("shared"):
+                units.append(("shared.", m["shared"]["ff"]))
+                t[p + "mlp.shared.sg"] = [1, E]
+            for u, f in units:
+                t.update({p + "mlp." + u + "gate": [f, E], p + "mlp." + u + "up": [f, E], p + "mlp." + u + "down": [E, f]})
+            t[p + "mlp.router"] = [m["router"]["experts"], E]
+        t[p + "dwa"] = [i + 2]
+    norm("final.norm")
+    t["head"] = [V, E]
+    return t
+
+
 def n_layer_runs(cfg: dict) -> int:
     lp = cfg.get("loop")
     return len(cfg["layers"]) + ((lp["stop"] - lp["start"]) * (lp["times"] - 1) if lp else 0)
@@ -102,6 +166,8 @@ def dopilorn_shapes(cfg: dict) -> Dict[str, List[int]]:
 def tensor_shapes(cfg: dict) -> Dict[str, List[int]]:
     if cfg.get("architecture") == "Dopilorn":
         return dopilorn_shapes(cfg)
+    if cfg.get("architecture") == "Tosevik":
+        return tosevik_shapes(cfg)
     E, V = cfg["width"], cfg["vocab"]
     t = {"embed": [V, E]}
     for i, L in enumerate(cfg["layers"]):
@@ -149,7 +215,16 @@ def synth_stack(d: str, cfg: dict, seed: int = 1234) -> str:
         for name, shp in shapes.items():
             n = int(np.prod(shp))
             zero_centred = cfg.get("architecture") == "Dopilorn" and name.rsplit(".", 1)[-1] in ("norm1", "norm2") or name == "final.norm" and cfg.get("architecture") == "Dopilorn"
-            if name.endswith("mlp.act"):
+            leaf = name.rsplit(".", 1)[-1]
+            if cfg.get("architecture") == "Tosevik" and leaf in ("b", "alpha", "dwa", "pb"):
+                if leaf == "dwa":                                # mostly the layer's own result, a little of every earlier one
+                    x = (0.3 / math.sqrt(n)) * rng.standard_normal(n, dtype=np.float32)
+                    x[-1] += 1.0
+                elif leaf == "alpha":
+                    x = np.full(1, 0.75, np.float32)
+                else:
+                    x = 0.1 * rng.standard_normal(n, dtype=np.float32) - (1.0 if leaf == "pb" else 0.0)
+            elif name.endswith("mlp.act"):
                 x = np.array([1.0, 0.5, 0.25, 0.0], np.float32)
             elif "canon" in name or zero_centred or name == "loop.step":
                 x = 0.1 * rng.standard_normal(n, dtype=np.float32)
