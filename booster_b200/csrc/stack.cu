@@ -180,6 +180,8 @@ struct StackCtx {
     float * keep = nullptr;               // depth average: [layers + 1][cap][E] results of this pass's tokens
     float * Xp = nullptr, * Ap = nullptr, * Yk = nullptr, * r_wt = nullptr, * r_sg = nullptr;      // routed mixture: rows by slot, weights, shared gate
     int32_t * r_sel = nullptr, * r_slot = nullptr, * r_src = nullptr, * r_seg = nullptr;
+    float * r_z = nullptr;                // router logits [cap][experts + 1]
+    int * r_counter = nullptr;            // per token: router blocks done
     float * da_part = nullptr;            // key-slice partials of the differential / sigmoid attention (few-token steps)
     int * da_counter = nullptr;           // per (token, head): slices done
     int sm_count = 148;
@@ -1114,7 +1116,7 @@ void mixer_retention(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T
     const int E = c->m->E, H = L.H, D = L.D, V = L.V, HD = H * D, HV = H * V, ldp = L.proj.N;
     float * S = c->rec + R.off_rec;
     linear(c, c->in, E, L.proj, c->P, ldp, T);
-    k_retention_prep<<<T, 128, 0, c->st>>>(c->P, ldp, 0, HD, H, D, RopeArgs{L.rope_freq, L.rope_dims, 1.0f}, L.k_scale, &c->d_step->st);
+    k_retention_prep<<<dim3((unsigned) T, (unsigned) ((2 * H + 3) / 4)), 128, 0, c->st>>>(c->P, ldp, 0, HD, H, D, RopeArgs{L.rope_freq, L.rope_dims, 1.0f}, L.k_scale, &c->d_step->st);
     if (D <= 32) launch_retention_scan<32>(c, L, T, ldp, S);
     else if (D <= 64) launch_retention_scan<64>(c, L, T, ldp, S);
     else if (D <= 128) launch_retention_scan<128>(c, L, T, ldp, S);
@@ -1298,8 +1300,8 @@ void enqueue_layers_parallel(StackCtx * c, int T) {
 // shared unit's in c->Y; the layer's join weighs and adds them
 void mixture_ff(StackCtx * c, const LayerSpec & L, int T, const int32_t ** slot_of) {
     const int E = c->m->E, top = L.top, ff = L.e_ff, slots = T * top;
-    const RouteArgs ra{c->Hn, E, E, L.router, L.w_sg, L.n_exp, top, L.n_groups, L.keep_groups, L.r_scale, c->r_sel, c->r_wt, c->r_sg};
-    k_moe_route<<<T, 256, (size_t) (2 * L.n_exp + L.n_groups) * 4, c->st>>>(ra);
+    const RouteArgs ra{c->Hn, E, E, L.router, L.w_sg, L.n_exp, top, L.n_groups, L.keep_groups, L.r_scale, c->r_sel, c->r_wt, c->r_sg, c->r_z, c->r_counter};
+    k_moe_route<<<dim3((unsigned) T, (unsigned) ((L.n_exp + (L.w_sg ? 1 : 0) + 7) / 8)), 256, (size_t) (2 * L.n_exp + L.n_groups) * 4, c->st>>>(ra);
     c->launches++;
     LinOpt o;
     o.alpha = 1.f; o.shift = 0.f;               // silu(gate) * up, no clamp
@@ -1312,7 +1314,11 @@ void mixture_ff(StackCtx * c, const LayerSpec & L, int T, const int32_t ** slot_
         *slot_of = nullptr;
     } else {
         // prompt portion: rows sorted by expert, one segmented product per projection
-        k_moe_sort<<<1, 256, (size_t) L.n_exp * 4, c->st>>>(c->r_sel, slots, top, L.n_exp, c->r_seg, c->r_slot, c->r_src);
+        int tpe = 1;
+        while (tpe * 2 * L.n_exp <= 1024 && tpe * 2 <= slots) tpe *= 2;
+        const size_t cnt_bytes = (size_t) L.n_exp * tpe * 4;
+        const int in_smem = (size_t) slots * 4 + cnt_bytes <= 40 * 1024 ? 1 : 0;
+        k_moe_sort<<<1, 1024, cnt_bytes + (in_smem ? (size_t) slots * 4 : 0), c->st>>>(c->r_sel, slots, top, L.n_exp, tpe, in_smem, c->r_seg, c->r_slot, c->r_src);
         k_gather_rows<<<slots, 128, 0, c->st>>>(c->Hn, E, c->r_src, E, c->Xp);
         c->launches += 2;
         o.seg = c->r_seg;
@@ -1478,7 +1484,8 @@ void stack_ctx_free(StackCtx * c) {
     if (c->g_token) cudaGraphExecDestroy(c->g_token);
     if (c->g_greedy) cudaGraphExecDestroy(c->g_greedy);
     cudaFree(c->d_out_tokens); cudaFree(c->d_counter);
-    for (float * p : { c->Y2, c->U, c->XC, c->keep, c->Xp, c->Ap, c->Yk, c->r_wt, c->r_sg }) cudaFree(p);
+    for (float * p : { c->Y2, c->U, c->XC, c->keep, c->Xp, c->Ap, c->Yk, c->r_wt, c->r_sg, c->r_z }) cudaFree(p);
+    cudaFree(c->r_counter);
     for (int32_t * p : { c->r_sel, c->r_slot, c->r_src, c->r_seg }) cudaFree(p);
     for (float * p : { c->X, c->Hn, c->Y, c->P, c->A, c->QK, c->OL, c->CV, c->BG, c->O, c->rec, c->d_logits }) cudaFree(p);
     for (float * p : c->cache_allocs) cudaFree(p);
@@ -1511,7 +1518,7 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
         if (m->max_slots > 0) {
             moe_rows = cap * (size_t) m->max_slots;
             fl(&c->Xp, moe_rows * m->E); fl(&c->Ap, moe_rows * m->max_eff); fl(&c->Yk, moe_rows * m->E);
-            fl(&c->r_wt, moe_rows); fl(&c->r_sg, cap);
+            fl(&c->r_wt, moe_rows); fl(&c->r_sg, cap); fl(&c->r_z, cap * ((size_t) m->max_exp + 1)); fl((float **) &c->r_counter, cap);
             fl((float **) &c->r_sel, moe_rows); fl((float **) &c->r_slot, moe_rows); fl((float **) &c->r_src, moe_rows); fl((float **) &c->r_seg, (size_t) m->max_exp + 1);
         }
         fl(&c->P, cap * m->maxP); fl(&c->A, cap * m->maxA); fl(&c->QK, cap_t * m->maxQK); fl(&c->OL, cap_t * m->maxOL);

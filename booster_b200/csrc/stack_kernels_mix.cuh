@@ -47,7 +47,7 @@ __global__ void k_dyt_rows(const float * __restrict__ X, int ldx, const int32_t 
 // v <- sum_(j < n_keep) coef[j] keep[j][t] (planes of `plane` floats; plane 0 is the embedding output); X[t] = v; and
 // Hn[t] = dyt(v) for the sub-layer that follows. grid (T, slices of JOIN_SLICE entries); a pair's two sums of squares are taken
 // by every slice's block over the whole row.
-constexpr int JOIN_SLICE = 1024;
+constexpr int JOIN_SLICE = 256;        // one entry per thread: a one-token step still spreads over several SMs
 struct JoinArgs {
     float * X; int E;
     const float * Ya; const float * Yb; const float * wa; const float * wb; float eps;      // Yb != nullptr: pair
@@ -98,11 +98,11 @@ __global__ void __launch_bounds__(256) k_join(const JoinArgs a) {
 // ---- retention: S <- decay_h S + k v^T, o = S^T q per head; no soft-max, no denominator --------------------------------------------
 // P[t] = [ q: H x D | k: H x D | v: H x V | output-gate pre-activation: H x V ].
 // Step 1, per token, in place: the first rope.dims entries of every q and k head are rotated by the token's position
-// ('rotate half' pairs), then k is scaled by k_scale (D^(-1/2)). One block per token, a warp per head.
+// ('rotate half' pairs), then k is scaled by k_scale (D^(-1/2)). grid (T, ceil(2 H / warps per block)): a warp per head.
 __global__ void k_retention_prep(float * __restrict__ P, int ldp, int q_off, int k_off, int H, int D, RopeArgs rope, float k_scale, const StepState * __restrict__ st) {
     const int t = blockIdx.x, pos = st->pos0 + t;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5, half = rope.dims / 2;
-    for (int v = warp; v < 2 * H; v += nw) {
+    for (int v = blockIdx.y * nw + warp; v < 2 * H; v += gridDim.y * nw) {
         const bool is_k = v >= H;
         float * x = P + (size_t) t * ldp + (is_k ? k_off + (size_t) (v - H) * D : q_off + (size_t) v * D);
         const float f = is_k ? k_scale : 1.0f;
@@ -348,45 +348,65 @@ __global__ void k_group_o_layout(const float * __restrict__ Or, int Tpad, int H,
 // neighbours; a group's score is its largest s; only experts of the `keep` best groups are eligible; the `top` eligible experts
 // with the largest s are chosen (lowest index first among equals) with weights s * scale, not renormalised.
 // sel[t][top], wt[t][top]; sg[t] = sigmoid(w_sg . h) is the shared unit's gate (w_sg == nullptr: no shared unit).
-// One block per token; dynamic shared memory: 2 n + n_groups floats.
+// grid (T, ceil(rows / 8)) with rows = n (+ 1 for the shared gate): a warp per row of the router, several 16-byte loads in flight;
+// the logits go to z[t][n + 1], and the block of a token that finishes last (an atomic counter, no waiting) makes the choice with
+// one warp. Dynamic shared memory: 2 n + n_groups floats.
 struct RouteArgs {
     const float * Hn; int ld, E;
     const float * Wr; const float * w_sg;
     int n, top, n_groups, keep;
     float scale;
     int32_t * sel; float * wt; float * sg;
+    float * z; int * counter;
 };
 __global__ void __launch_bounds__(256) k_moe_route(const RouteArgs a) {
     extern __shared__ float rsm[];
+    __shared__ int last_s;
     float * s = rsm, * elig = rsm + a.n, * gbest = rsm + 2 * a.n;
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float * h = a.Hn + (size_t) t * a.ld;
-    for (int e = warp; e < a.n + (a.w_sg ? 1 : 0); e += nw) {
+    const int rows = a.n + (a.w_sg ? 1 : 0), e = blockIdx.y * 8 + warp;
+    float * z = a.z + (size_t) t * (a.n + 1);
+    if (e < rows) {
         const float * w = e < a.n ? a.Wr + (size_t) e * a.E : a.w_sg;
-        float acc = 0.f;
-        for (int i = lane; i < a.E; i += 32) acc = fmaf(w[i], h[i], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) { if (e < a.n) s[e] = acc; else a.sg[t] = sigmoidf_(acc); }
+        float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+        if ((a.E & 3) == 0 && (a.ld & 3) == 0 && (((uintptr_t) w | (uintptr_t) h) & 15) == 0) {
+#pragma unroll 4
+            for (int i = lane * 4; i < a.E; i += 128) {
+                const float4 x = *reinterpret_cast<const float4 *>(h + i), y = __ldg(reinterpret_cast<const float4 *>(w + i));
+                acc0 = fmaf(x.x, y.x, acc0); acc1 = fmaf(x.y, y.y, acc1); acc2 = fmaf(x.z, y.z, acc2); acc3 = fmaf(x.w, y.w, acc3);
+            }
+        } else {
+            for (int i = lane; i < a.E; i += 32) acc0 = fmaf(w[i], h[i], acc0);
+        }
+        const float acc = warp_sum((acc0 + acc1) + (acc2 + acc3));
+        if (lane == 0) { if (e < a.n) z[e] = acc; else a.sg[t] = sigmoidf_(acc); }
     }
-    __syncthreads();
+    if (gridDim.y > 1) {
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) last_s = atomicAdd(a.counter + t, 1) == (int) gridDim.y - 1;
+        __syncthreads();
+        if (!last_s) return;
+        __threadfence();
+        if (threadIdx.x == 0) a.counter[t] = 0;
+    } else __syncthreads();
     if (warp != 0) return;
     float mx = -INFINITY;
-    for (int e = lane; e < a.n; e += 32) mx = fmaxf(mx, s[e]);
+    for (int i = lane; i < a.n; i += 32) { const float v = __ldcg(z + i); s[i] = v; mx = fmaxf(mx, v); }
     mx = warp_max(mx);
     float sum = 0.f;
-    for (int e = lane; e < a.n; e += 32) { const float v = expf(s[e] - mx); s[e] = v; sum += v; }
+    for (int i = lane; i < a.n; i += 32) { const float v = expf(s[i] - mx); s[i] = v; sum += v; }
     sum = warp_sum(sum);
     const float inv = 1.0f / sum;
-    __syncwarp();
     const int per = a.n / a.n_groups;
-    for (int e = lane; e < a.n; e += 32) s[e] *= inv;
+    for (int i = lane; i < a.n; i += 32) { s[i] *= inv; elig[i] = -1.f; }
     __syncwarp();
     for (int g = lane; g < a.n_groups; g += 32) {
         float b = -1.f;
         for (int i = 0; i < per; i++) b = fmaxf(b, s[g * per + i]);
         gbest[g] = b;
     }
-    for (int e = lane; e < a.n; e += 32) elig[e] = -1.f;
     __syncwarp();
     // the best groups, one at a time; then the best eligible experts, one at a time (value, then lowest index)
     for (int r = 0; r < a.keep; r++) {
@@ -404,7 +424,7 @@ __global__ void __launch_bounds__(256) k_moe_route(const RouteArgs a) {
     }
     for (int r = 0; r < a.top; r++) {
         float bv = -0.5f; int bi = 0x7fffffff;
-        for (int e = lane; e < a.n; e += 32) if (elig[e] > bv) { bv = elig[e]; bi = e; }
+        for (int i = lane; i < a.n; i += 32) if (elig[i] > bv) { bv = elig[i]; bi = i; }
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
@@ -415,25 +435,52 @@ __global__ void __launch_bounds__(256) k_moe_route(const RouteArgs a) {
     }
 }
 // Prompt portions: the n_slots = T top (token, choice) slots sorted by expert, stably, so that every expert's rows are contiguous:
-// seg[e] .. seg[e + 1] - 1 are expert e's rows, slot_of[slot] the row a slot got, src_row[row] the token it reads. One block; a
-// thread per expert walks the slots in order.
-__global__ void k_moe_sort(const int32_t * __restrict__ sel, int n_slots, int top, int n, int32_t * __restrict__ seg, int32_t * __restrict__ slot_of, int32_t * __restrict__ src_row) {
-    extern __shared__ int cnt[];
-    for (int e = threadIdx.x; e < n; e += blockDim.x) {
+// seg[e] .. seg[e + 1] - 1 are expert e's rows, slot_of[slot] the row a slot got, src_row[row] the token it reads. One block of
+// 1024 threads: `tpe` threads per expert (a power of two) each count one contiguous part of the slots, a block-wide prefix sum
+// over (expert, part) gives every thread its first row, a second walk places the slots. Dynamic shared memory: the slots'
+// experts when they fit (in_smem), then n tpe counters.
+__global__ void __launch_bounds__(1024) k_moe_sort(const int32_t * __restrict__ sel, int n_slots, int top, int n, int tpe, int in_smem,
+                                                   int32_t * __restrict__ seg, int32_t * __restrict__ slot_of, int32_t * __restrict__ src_row) {
+    extern __shared__ int ssm[];
+    __shared__ int wsum[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int * cnt = ssm + (in_smem ? n_slots : 0);
+    const int32_t * es = sel;
+    if (in_smem) {
+        for (int i = tid; i < n_slots; i += 1024) ssm[i] = sel[i];
+        es = ssm;
+    }
+    __syncthreads();
+    const int chunk = (n_slots + tpe - 1) / tpe, part = tid & (tpe - 1), epb = 1024 / tpe;
+    const int s0 = min(part * chunk, n_slots), s1 = min(s0 + chunk, n_slots);
+    for (int e = tid / tpe; e < n; e += epb) {
         int c = 0;
-        for (int s = 0; s < n_slots; s++) c += sel[s] == e;
-        cnt[e] = c;
+        for (int i = s0; i < s1; i++) c += es[i] == e;
+        cnt[e * tpe + part] = c;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int at = 0;
-        for (int e = 0; e < n; e++) { seg[e] = at; at += cnt[e]; }
-        seg[n] = at;
+    // exclusive prefix sum over the M = n tpe counters, in place: a thread owns `own` consecutive entries
+    const int M = n * tpe, own = (M + 1023) / 1024, b0 = min(tid * own, M), b1 = min(b0 + own, M);
+    int mine = 0;
+    for (int i = b0; i < b1; i++) mine += cnt[i];
+    int inc = mine;
+    for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= o) inc += v; }
+    if (lane == 31) wsum[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int v = wsum[lane];
+        for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
+        wsum[lane] = v;
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < n; e += blockDim.x) {
-        int at = seg[e];
-        for (int s = 0; s < n_slots; s++) if (sel[s] == e) { slot_of[s] = at; src_row[at] = s / top; at++; }
+    int at = inc - mine + (warp ? wsum[warp - 1] : 0);
+    for (int i = b0; i < b1; i++) { const int c = cnt[i]; cnt[i] = at; at += c; }
+    __syncthreads();
+    for (int e = tid; e < n; e += 1024) seg[e] = cnt[e * tpe];
+    if (tid == 0) seg[n] = n_slots;
+    for (int e = tid / tpe; e < n; e += epb) {
+        int r = cnt[e * tpe + part];
+        for (int i = s0; i < s1; i++) if (es[i] == e) { slot_of[i] = r; src_row[r] = i / top; r++; }
     }
 }
 // Y[r] = X[src_row[r]]
