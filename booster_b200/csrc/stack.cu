@@ -3,13 +3,17 @@
 // the registry of designs and mixers. Kernels: stack_kernels.cuh. C-ABI dispatch: engine.cu.
 //
 // A design is a name in config.json ("architecture") mapped to a builder that turns the configuration into a list of
-// LayerSpec; a mixer is a name ("type") mapped to a loader of its tensors and a forward routine. Two designs are registered:
+// LayerSpec; a mixer is a name ("type") mapped to a loader of its tensors and a forward routine. Three designs are registered:
 //   Matulorn   sequential sub-layers with grouped norms before and after each; mixers minGRU | latent attention (rotated
 //              part, window, sink) | gated delta rule; clamped gated feed-forward
 //   Dopilorn   both sub-layers read the same residual (x += mixer(n1 x) + ff(n2 x)) behind a causal convolution of their
 //              inputs; mixers latent attention (query latent, head gates) | generalized delta rule | differential
 //              sliding-window attention; polynomial feed-forward; a span of layers run several times with the same weights
 //              (each pass with a state of its own); soft-capped logits
+//   Tosevik    pre-norm sub-layers with element-wise norms (dynamic tanh); after every layer the stream becomes a weighted sum of
+//              the embedding output and all layers' results so far; mixers retention | parallel (sigmoid attention with a distance
+//              penalty beside a retention, each normed, averaged); routed mixture of gated units with group-limited choice and a
+//              gated shared unit
 // A model is executed as a list of layer RUNS: (layer, state slot), one per layer unless the design repeats some.
 #include "stack.hpp"
 #include "safetensors.hpp"

@@ -3,7 +3,8 @@
 // gated delta rule | generalized delta rule | differential sliding-window attention) and an optional feed-forward
 // (clamped gated unit | polynomial activation with norms), either one sub-layer after the other with grouped RMS norms
 // before and after each, or both reading the same residual behind causal convolutions of their normed inputs.
-// Every size and constant is a kernel argument; nothing is specialised for one model.
+// Every size and constant is a kernel argument; nothing is specialised for one model. stack_kernels_mix.cuh holds the kernels of
+// further mechanisms (element-wise norm, depth average, retention, sigmoid attention, routed mixture) on top of these.
 //
 // Precision: the residual stream, norms, positions and angles, attention scores and weights, recurrent states and
 // everything that enters a recurrence are float32. Matrix products take float32 activations and weights in the
