@@ -1120,6 +1120,20 @@ void mixer_retention(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T
     const int E = c->m->E, H = L.H, D = L.D, V = L.V, HD = H * D, HV = H * V, ldp = L.proj.N;
     float * S = c->rec + R.off_rec;
     linear(c, c->in, E, L.proj, c->P, ldp, T);
+    if (T == 1) {
+        // one token: rotation, state update, read-out norm and gate in one launch, a block per head
+        const RopeArgs rope{L.rope_freq, L.rope_dims, 1.0f};
+        const int threads = GD_RG * std::min(128, (V + 7) / 8 * 8);
+        const size_t sm = (size_t) V * 4;
+        const StepState * st = &c->d_step->st;
+        if (D <= 32) k_retention_token<32><<<H, threads, sm, c->st>>>(c->P, 0, HD, 2 * HD, 2 * HD + HV, L.decay, rope, L.k_scale, st, H, D, V, c->m->eps, S, c->A);
+        else if (D <= 64) k_retention_token<64><<<H, threads, sm, c->st>>>(c->P, 0, HD, 2 * HD, 2 * HD + HV, L.decay, rope, L.k_scale, st, H, D, V, c->m->eps, S, c->A);
+        else if (D <= 128) k_retention_token<128><<<H, threads, sm, c->st>>>(c->P, 0, HD, 2 * HD, 2 * HD + HV, L.decay, rope, L.k_scale, st, H, D, V, c->m->eps, S, c->A);
+        else k_retention_token<256><<<H, threads, sm, c->st>>>(c->P, 0, HD, 2 * HD, 2 * HD + HV, L.decay, rope, L.k_scale, st, H, D, V, c->m->eps, S, c->A);
+        c->launches++;
+        linear(c, c->A, HV, L.o, c->out, E, T);
+        return;
+    }
     k_retention_prep<<<dim3((unsigned) T, (unsigned) ((2 * H + 3) / 4)), 128, 0, c->st>>>(c->P, ldp, 0, HD, H, D, RopeArgs{L.rope_freq, L.rope_dims, 1.0f}, L.k_scale, &c->d_step->st);
     if (D <= 32) launch_retention_scan<32>(c, L, T, ldp, S);
     else if (D <= 64) launch_retention_scan<64>(c, L, T, ldp, S);

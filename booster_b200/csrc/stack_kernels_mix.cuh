@@ -174,6 +174,72 @@ __global__ void __launch_bounds__(512) k_retention_scan(const float * __restrict
     }
 }
 
+// The whole mixer core for a one-token step in one launch (steps 1 and 2 and the read-out's norm and gate): one block per head.
+// Rotation and key scale happen on the way into shared memory, the state is updated tile by tile of up to 128 columns (the same
+// four-lanes-per-column layout), the head's read-out is kept in shared memory, then A[h] = o / rms(o) * silu(gate) (eps inside the
+// root, no weight). Dynamic shared memory: V floats.
+template <int DMAX>
+__global__ void __launch_bounds__(512) k_retention_token(const float * __restrict__ P, int q_off, int k_off, int v_off, int g_off, const float * __restrict__ decay,
+                                                         RopeArgs rope, float k_scale, const StepState * __restrict__ st, int H, int D, int V, float eps,
+                                                         float * __restrict__ S, float * __restrict__ A) {
+    constexpr int DR = DMAX / GD_RG, ROW = GD_RG * (DR + GD_PAD);
+    extern __shared__ float o_s[];                      // [V]
+    __shared__ __align__(16) float qs[ROW], ks[ROW];
+    __shared__ float red[16];
+    const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, rg = lane & 3, ncols = blockDim.x / GD_RG;
+    const int pos = st->pos0, half = rope.dims / 2;
+    const float * q = P + q_off + (size_t) h * D, * k = P + k_off + (size_t) h * D;
+    for (int i = tid; i < 2 * DMAX; i += blockDim.x) {
+        const bool is_k = i >= DMAX;
+        const int d = is_k ? i - DMAX : i, at = (d / DR) * (DR + GD_PAD) + d % DR;
+        float v = 0.f;
+        if (d < D) {
+            const float * x = is_k ? k : q;
+            if (d < half) { float a, b; rope_pair(rope, pos, d, x[d], x[d + half], a, b); v = a; }
+            else if (d < rope.dims) { float a, b; rope_pair(rope, pos, d - half, x[d - half], x[d], a, b); v = b; }
+            else v = x[d];
+            if (is_k) v *= k_scale;
+        }
+        (is_k ? ks : qs)[at] = v;
+    }
+    __syncthreads();
+    const float g = decay[h];
+    float * Sh = S + (size_t) h * D * V;
+    const int base = rg * (DR + GD_PAD), cl = warp * 8 + (lane >> 2);
+    float ss = 0.f;
+    for (int c0 = 0; c0 < V; c0 += ncols) {
+        const int col = c0 + cl;
+        const bool live = col < V;
+        const float v = live ? P[v_off + (size_t) h * V + col] : 0.f;
+        float op[4] = { 0.f, 0.f, 0.f, 0.f };
+        constexpr int CH = DR < 16 ? DR : 16;           // rows whose loads are in flight together (the stores would order them otherwise)
+#pragma unroll 1
+        for (int i0 = 0; i0 < DR; i0 += CH) {
+            float sv[CH];
+#pragma unroll
+            for (int i = 0; i < CH; i++) { const int d = rg * DR + i0 + i; sv[i] = (live && d < D) ? Sh[(size_t) d * V + col] : 0.f; }
+#pragma unroll
+            for (int i = 0; i < CH; i++) {
+                const int d = rg * DR + i0 + i;
+                sv[i] = fmaf(g, sv[i], ks[base + i0 + i] * v);
+                if (live && d < D) Sh[(size_t) d * V + col] = sv[i];
+                op[i & 3] = fmaf(sv[i], qs[base + i0 + i], op[i & 3]);
+            }
+        }
+        float o = (op[0] + op[1]) + (op[2] + op[3]);
+        o += __shfl_xor_sync(0xffffffffu, o, 1);
+        o += __shfl_xor_sync(0xffffffffu, o, 2);
+        if (rg == 0 && live) { o_s[col] = o; ss = fmaf(o, o, ss); }
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int w = 0; w < (int) (blockDim.x >> 5); w++) tot += red[w];
+    const float r = 1.0f / sqrtf(tot / (float) V + eps);
+    for (int i = tid; i < V; i += blockDim.x) A[(size_t) h * V + i] = o_s[i] * r * siluf_(P[g_off + (size_t) h * V + i]);
+}
+
 // ---- sigmoid attention over grouped key/value heads -------------------------------------------------------------------------------
 // P[t] = [ q: H x D | k: G x D | v: G x V ]. Query head h reads key/value head h / (H / G); position p sees every j <= p.
 // The weight of key j for head h is sigmoid((q . k_j) scale - slope[h] (p - j) + pb[h]); weights are not normalised over keys.
@@ -253,6 +319,12 @@ __global__ void __launch_bounds__(256) k_sig_attn(const SigAttnArgs a) {
             const int jb = c * 32, j = jb + lane, cnt = min(32, p - jb + 1);
             float w = 0.f;
             if (lane < cnt) {
+                // the lane's key row and value row are asked for now, whole: the dot product and the weighted sum then find them in L2
+                // instead of paying one memory round trip per batch of loads
+                const char * kp = reinterpret_cast<const char *>(a.cache + (size_t) j * a.ldc + koff);
+                const char * vp = reinterpret_cast<const char *>(a.cache + (size_t) j * a.ldc + voff);
+                for (int b = 128; b < a.D * 4; b += 128) asm volatile("prefetch.global.L2 [%0];" :: "l"(kp + b));
+                for (int b = 0; b < a.V * 4; b += 128) asm volatile("prefetch.global.L2 [%0];" :: "l"(vp + b));
                 const float * k1 = a.cache + (size_t) j * a.ldc + koff;
                 float x0 = 0.f, x1 = 0.f;
                 if (a.vec) {
@@ -268,7 +340,7 @@ __global__ void __launch_bounds__(256) k_sig_attn(const SigAttnArgs a) {
                 w = sigmoidf_(fmaf(x0 + x1, a.scale, pb - slope * (float) (p - j)));
             }
             const float * vrow = a.cache + (size_t) jb * a.ldc + voff;
-#pragma unroll 4
+#pragma unroll 8
             for (int kk = 0; kk < cnt; kk++) {
                 const float wk = __shfl_sync(0xffffffffu, w, kk);
 #pragma unroll
