@@ -133,6 +133,8 @@ struct StackModel {
     bool depth_avg = false;               // every layer hands on a weighted sum of all results so far
     bool has_pair = false;
     int max_slots = 0, max_eff = 0, max_exp = 0;      // routed mixtures: choices per token, expert width, experts
+    size_t max_ret_state = 0;             // retention: the largest heads x dim x vdim
+    int max_ret_dim = 0;
     DMat loop_in;                         // repeated span: [E][2 E]
     float * loop_step = nullptr;          // [times][E]
     std::vector<LayerSpec> layers;
@@ -181,6 +183,7 @@ struct StackCtx {
     size_t att_scores_floats = 0;
     std::vector<float *> cache_allocs;    // the caches with their zero margins (caches[] point behind the front margin)
     float * att_part = nullptr, * att_ml = nullptr;   // key-slice partials of the latent attention (decode)
+    float * ret_sb = nullptr;             // retention, long portions: per-chunk states [heads][chunks][dim][vdim]
     float * keep = nullptr;               // depth average: [layers + 1][cap][E] results of this pass's tokens
     float * Xp = nullptr, * Ap = nullptr, * Yk = nullptr, * r_wt = nullptr, * r_sg = nullptr;      // routed mixture: rows by slot, weights, shared gate
     int32_t * r_sel = nullptr, * r_slot = nullptr, * r_src = nullptr, * r_seg = nullptr;
@@ -456,6 +459,7 @@ void load_retention(StackModel & m, LayerSpec & L, const Json & mx, const safete
     L.o = up_mat(m, sf.read_f32(p + "o", {E, H * V}), E, H * V, nullptr);
     L.n_rec = (size_t) H * D * V;
     m.maxP = std::max(m.maxP, L.proj.N); m.maxA = std::max(m.maxA, H * V);
+    m.max_ret_state = std::max(m.max_ret_state, L.n_rec); m.max_ret_dim = std::max(m.max_ret_dim, D);
 }
 
 // sigmoid attention: '<prefix>{q,k,v,q.norm,k.norm,pb,o}'; slopes 2^(-8 (h + 1) / H) are fixed by the mechanism
@@ -1105,6 +1109,13 @@ void mixer_diffattn(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T)
     linear(c, c->A, H * V, L.o, c->out, E, T);
 }
 
+constexpr int RET_CHUNK_MIN_T = 128;      // shorter portions walk token by token
+size_t retention_chunk_smem(int D) { return ((size_t) 2 * RC * (D + 4) + (size_t) RC * (RC + 1) + (size_t) RC * 128 + RC + 1) * 4; }
+bool retention_chunks_enabled() {
+    static const bool on = [] { const char * e = std::getenv("BOOSTER_B200_STACK_RET_CHUNKS"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
 template <int DMAX>
 void launch_retention_scan(StackCtx * c, const LayerSpec & L, int T, int ldp, float * S) {
     // four lanes per column of the state; a head's columns are spread over blocks of >= 16 until the grid fills the SMs
@@ -1135,7 +1146,17 @@ void mixer_retention(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T
         return;
     }
     k_retention_prep<<<dim3((unsigned) T, (unsigned) ((2 * H + 3) / 4)), 128, 0, c->st>>>(c->P, ldp, 0, HD, H, D, RopeArgs{L.rope_freq, L.rope_dims, 1.0f}, L.k_scale, &c->d_step->st);
-    if (D <= 32) launch_retention_scan<32>(c, L, T, ldp, S);
+    if (T >= RET_CHUNK_MIN_T && c->ret_sb && retention_chunks_enabled()) {
+        // long portions: per-chunk products in parallel, a short walk over the chunks in between
+        const int nch = (T + RC - 1) / RC, vt = (V + 127) / 128;
+        const dim3 grid((unsigned) H, (unsigned) nch, (unsigned) vt);
+        const size_t sm = retention_chunk_smem(D);
+        k_retention_chunk_kv<<<grid, 256, 0, c->st>>>(c->P, ldp, HD, 2 * HD, L.decay, T, H, D, V, c->ret_sb);
+        k_retention_chunk_state<<<dim3((unsigned) H, (unsigned) ((D * V + 255) / 256)), 256, 0, c->st>>>(L.decay, T, D, V, nch, S, c->ret_sb);
+        k_retention_chunk_out<<<grid, 128, sm, c->st>>>(c->P, ldp, 0, HD, 2 * HD, L.decay, T, H, D, V, c->ret_sb, c->O);
+        c->launches += 2;
+    }
+    else if (D <= 32) launch_retention_scan<32>(c, L, T, ldp, S);
     else if (D <= 64) launch_retention_scan<64>(c, L, T, ldp, S);
     else if (D <= 128) launch_retention_scan<128>(c, L, T, ldp, S);
     else launch_retention_scan<256>(c, L, T, ldp, S);
@@ -1502,7 +1523,7 @@ void stack_ctx_free(StackCtx * c) {
     if (c->g_token) cudaGraphExecDestroy(c->g_token);
     if (c->g_greedy) cudaGraphExecDestroy(c->g_greedy);
     cudaFree(c->d_out_tokens); cudaFree(c->d_counter);
-    for (float * p : { c->Y2, c->U, c->XC, c->keep, c->Xp, c->Ap, c->Yk, c->r_wt, c->r_sg, c->r_z }) cudaFree(p);
+    for (float * p : { c->Y2, c->U, c->XC, c->keep, c->ret_sb, c->Xp, c->Ap, c->Yk, c->r_wt, c->r_sg, c->r_z }) cudaFree(p);
     cudaFree(c->r_counter);
     for (int32_t * p : { c->r_sel, c->r_slot, c->r_src, c->r_seg }) cudaFree(p);
     for (float * p : { c->X, c->Hn, c->Y, c->P, c->A, c->QK, c->OL, c->CV, c->BG, c->O, c->rec, c->d_logits }) cudaFree(p);
@@ -1532,6 +1553,12 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
         if (par) { fl(&c->Y2, cap * m->E); fl(&c->U, cap * m->E * 2); fl(&c->XC, cap * m->E * 2); }
         else if (m->has_pair) fl(&c->Y2, cap * m->E);
         if (m->depth_avg) fl(&c->keep, (m->layers.size() + 1) * cap * m->E);
+        if (m->max_ret_state > 0 && c->cap >= RET_CHUNK_MIN_T) {
+            fl(&c->ret_sb, (size_t) ((c->cap + RC - 1) / RC) * m->max_ret_state);
+            static size_t attr = 48 * 1024;
+            const size_t need = retention_chunk_smem(m->max_ret_dim);
+            if (need > attr) { SCU(cudaFuncSetAttribute(k_retention_chunk_out, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) need)); attr = need; }
+        }
         size_t moe_rows = 0;
         if (m->max_slots > 0) {
             moe_rows = cap * (size_t) m->max_slots;

@@ -174,6 +174,158 @@ __global__ void __launch_bounds__(512) k_retention_scan(const float * __restrict
     }
 }
 
+// Long prompt portions run the same recurrence chunk by chunk (RC tokens), so that only the short walk over chunks is serial.
+// With t, j local to chunk c of n_c tokens, S_c the state before it and g the head's decay:
+//   U_c = sum_j g^(n_c - 1 - j) k_j v_j^T                               k_retention_chunk_kv     (all chunks at once)
+//   S_(c+1) = g^(n_c) S_c + U_c                                         k_retention_chunk_state  (in place: U_c's slot then holds S_c)
+//   o_t = g^(t + 1) S_c^T q_t + sum_(j <= t) g^(t - j) (q_t . k_j) v_j  k_retention_chunk_out    (all chunks at once)
+// Same float32 arithmetic as the walk, sums in another order. SB [H][chunks][D][V] is a working buffer of the pass.
+constexpr int RC = 32;
+// grid (H, chunks, ceil(V / 128)), 256 threads: thread (ty, tx) owns 8 x 8 of a 128 x 128 tile of U_c; keys and decay-scaled values
+// of the chunk are staged in shared memory
+__global__ void __launch_bounds__(256) k_retention_chunk_kv(const float * __restrict__ P, int ldp, int k_off, int v_off, const float * __restrict__ decay,
+                                                            int T, int H, int D, int V, float * __restrict__ SB) {
+    __shared__ __align__(16) float Ks[RC][128], Vs[RC][128];
+    const int h = blockIdx.x, c = blockIdx.y, v0 = blockIdx.z * 128, tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int t0 = c * RC, nt = min(RC, T - t0), nch = gridDim.y;
+    const float g = decay[h];
+    for (int i = tid; i < RC * 128; i += 256) {
+        const int j = i >> 7, v = v0 + (i & 127);
+        Vs[j][i & 127] = (j < nt && v < V) ? P[(size_t) (t0 + j) * ldp + v_off + (size_t) h * V + v] * powf(g, (float) (nt - 1 - j)) : 0.f;
+    }
+    float * U = SB + ((size_t) h * nch + c) * D * V;
+    for (int d0 = 0; d0 < D; d0 += 128) {
+        __syncthreads();
+        for (int i = tid; i < RC * 128; i += 256) {
+            const int j = i >> 7, d = d0 + (i & 127);
+            Ks[j][i & 127] = (j < nt && d < D) ? P[(size_t) (t0 + j) * ldp + k_off + (size_t) h * D + d] : 0.f;
+        }
+        __syncthreads();
+        float acc[8][8];
+#pragma unroll
+        for (int a = 0; a < 8; a++)
+#pragma unroll
+            for (int b = 0; b < 8; b++) acc[a][b] = 0.f;
+#pragma unroll 4
+        for (int j = 0; j < RC; j++) {
+            const float4 ka = *reinterpret_cast<const float4 *>(&Ks[j][ty * 8]), kb = *reinterpret_cast<const float4 *>(&Ks[j][ty * 8 + 4]);
+            const float4 va = *reinterpret_cast<const float4 *>(&Vs[j][tx * 8]), vb = *reinterpret_cast<const float4 *>(&Vs[j][tx * 8 + 4]);
+            const float kk[8] = { ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w }, vv[8] = { va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w };
+#pragma unroll
+            for (int a = 0; a < 8; a++)
+#pragma unroll
+                for (int b = 0; b < 8; b++) acc[a][b] = fmaf(kk[a], vv[b], acc[a][b]);
+        }
+#pragma unroll
+        for (int a = 0; a < 8; a++) {
+            const int d = d0 + ty * 8 + a;
+            if (d >= D) continue;
+#pragma unroll
+            for (int b = 0; b < 8; b++) { const int v = v0 + tx * 8 + b; if (v < V) U[(size_t) d * V + v] = acc[a][b]; }
+        }
+    }
+}
+// grid (H, ceil(D V / 256)): a thread owns one entry of the state and walks the chunks
+__global__ void k_retention_chunk_state(const float * __restrict__ decay, int T, int D, int V, int nch, float * __restrict__ S, float * __restrict__ SB) {
+    const int h = blockIdx.x, e = blockIdx.y * blockDim.x + threadIdx.x, n = D * V;
+    if (e >= n) return;
+    const float g = decay[h], gfull = powf(g, (float) RC), glast = powf(g, (float) (T - (nch - 1) * RC));
+    float s = S[(size_t) h * n + e];
+    float * sb = SB + (size_t) h * nch * n + e;
+    for (int c0 = 0; c0 < nch; c0 += 8) {
+        float u[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) u[i] = c0 + i < nch ? sb[(size_t) (c0 + i) * n] : 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            if (c0 + i < nch) {
+                sb[(size_t) (c0 + i) * n] = s;
+                s = fmaf(c0 + i == nch - 1 ? glast : gfull, s, u[i]);
+            }
+        }
+    }
+    S[(size_t) h * n + e] = s;
+}
+// grid (H, chunks, ceil(V / 128)), 128 threads: warp w owns tokens 8 w .. 8 w + 7 of the chunk, a lane four value channels.
+// Dynamic shared memory: q and k of the chunk [RC][D + 4] each, the masked scores [RC][RC + 1], the values [RC][128], the powers of g.
+__global__ void __launch_bounds__(128) k_retention_chunk_out(const float * __restrict__ P, int ldp, int q_off, int k_off, int v_off, const float * __restrict__ decay,
+                                                             int T, int H, int D, int V, const float * __restrict__ SB, float * __restrict__ O) {
+    extern __shared__ __align__(16) float csm[];
+    const int Dp = D + 4;
+    float * Qs = csm, * Ks = Qs + RC * Dp, * As = Ks + RC * Dp, * Vs = As + RC * (RC + 1), * pw = Vs + RC * 128;
+    const int h = blockIdx.x, c = blockIdx.y, v0 = blockIdx.z * 128, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int t0 = c * RC, nt = min(RC, T - t0), nch = gridDim.y;
+    const float g = decay[h];
+    for (int i = tid; i < RC * D; i += 128) {
+        const int j = i / D, d = i - j * D;
+        const float * p = P + (size_t) (t0 + (j < nt ? j : 0)) * ldp + (size_t) h * D + d;
+        Qs[j * Dp + d] = j < nt ? p[q_off] : 0.f;
+        Ks[j * Dp + d] = j < nt ? p[k_off] : 0.f;
+    }
+    for (int i = tid; i < RC * 128; i += 128) {
+        const int j = i >> 7, v = v0 + (i & 127);
+        Vs[i] = (j < nt && v < V) ? P[(size_t) (t0 + j) * ldp + v_off + (size_t) h * V + v] : 0.f;
+    }
+    if (tid <= RC) pw[tid] = powf(g, (float) tid);
+    __syncthreads();
+    {   // scores of the chunk against itself: thread -> token t = tid / 4, keys j = (tid % 4) * 8 .. + 7
+        const int t = tid >> 2, j0 = (tid & 3) * 8;
+        float sc[8] = { 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f };
+        for (int d = 0; d < D; d++) {
+            const float qv = Qs[t * Dp + d];
+#pragma unroll
+            for (int i = 0; i < 8; i++) sc[i] = fmaf(qv, Ks[(j0 + i) * Dp + d], sc[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) { const int j = j0 + i; As[t * (RC + 1) + j] = j <= t ? sc[i] * pw[t - j] : 0.f; }
+    }
+    __syncthreads();
+    float acc[8][4];
+#pragma unroll
+    for (int a = 0; a < 8; a++)
+#pragma unroll
+        for (int b = 0; b < 4; b++) acc[a][b] = 0.f;
+    const float * Sc = SB + ((size_t) h * nch + c) * D * V;
+    const int v = v0 + lane * 4;
+    const bool vec = (V & 3) == 0 && v + 3 < V;
+#pragma unroll 4
+    for (int d = 0; d < D; d++) {
+        float sv[4];
+        if (vec) { const float4 f = __ldg(reinterpret_cast<const float4 *>(Sc + (size_t) d * V + v)); sv[0] = f.x; sv[1] = f.y; sv[2] = f.z; sv[3] = f.w; }
+        else {
+#pragma unroll
+            for (int b = 0; b < 4; b++) sv[b] = v + b < V ? __ldg(Sc + (size_t) d * V + v + b) : 0.f;
+        }
+#pragma unroll
+        for (int a = 0; a < 8; a++) {
+            const float qv = Qs[(warp * 8 + a) * Dp + d];
+#pragma unroll
+            for (int b = 0; b < 4; b++) acc[a][b] = fmaf(qv, sv[b], acc[a][b]);
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < 8; a++) {
+        const float f = pw[warp * 8 + a + 1];
+#pragma unroll
+        for (int b = 0; b < 4; b++) acc[a][b] *= f;
+    }
+    for (int j = 0; j < RC; j++) {
+        const float4 f = *reinterpret_cast<const float4 *>(Vs + j * 128 + lane * 4);
+#pragma unroll
+        for (int a = 0; a < 8; a++) {
+            const float w = As[(warp * 8 + a) * (RC + 1) + j];
+            acc[a][0] = fmaf(w, f.x, acc[a][0]); acc[a][1] = fmaf(w, f.y, acc[a][1]); acc[a][2] = fmaf(w, f.z, acc[a][2]); acc[a][3] = fmaf(w, f.w, acc[a][3]);
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < 8; a++) {
+        const int tl = warp * 8 + a;
+        if (tl >= nt) continue;
+#pragma unroll
+        for (int b = 0; b < 4; b++) if (v + b < V) O[(size_t) (t0 + tl) * H * V + (size_t) h * V + v + b] = acc[a][b];
+    }
+}
+
 // The whole mixer core for a one-token step in one launch (steps 1 and 2 and the read-out's norm and gate): one block per head.
 // Rotation and key scale happen on the way into shared memory, the state is updated tile by tile of up to 128 columns (the same
 // four-lanes-per-column layout), the head's read-out is kept in shared memory, then A[h] = o / rms(o) * silu(gate) (eps inside the
