@@ -1110,7 +1110,7 @@ void mixer_diffattn(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T)
 }
 
 constexpr int RET_CHUNK_MIN_T = 128;      // shorter portions walk token by token
-size_t retention_chunk_smem(int D) { return ((size_t) 2 * RC * (D + 4) + (size_t) RC * (RC + 1) + (size_t) RC * 128 + RC + 1) * 4; }
+size_t retention_chunk_smem(int D) { return ((size_t) 2 * RC * (D + 4) + (size_t) RC * (RC + 4) + (size_t) RC * 128 + RC + 1) * 4; }
 bool retention_chunks_enabled() {
     static const bool on = [] { const char * e = std::getenv("BOOSTER_B200_STACK_RET_CHUNKS"); return !(e && e[0] == '0'); }();
     return on;

@@ -181,6 +181,28 @@ __global__ void __launch_bounds__(512) k_retention_scan(const float * __restrict
 //   o_t = g^(t + 1) S_c^T q_t + sum_(j <= t) g^(t - j) (q_t . k_j) v_j  k_retention_chunk_out    (all chunks at once)
 // Same float32 arithmetic as the walk, sums in another order. SB [H][chunks][D][V] is a working buffer of the pass.
 constexpr int RC = 32;
+// rows [0, n_rows) x columns [0, n_cols) of a row-major source into a shared tile of `rows` x `cols` (row stride dst_ld), zeros
+// elsewhere, by asynchronous copies that are all issued before any is awaited (16 bytes each when `vec`: every address a multiple of 16)
+__device__ __forceinline__ void stage_tile_async(float * dst, int dst_ld, const float * src, size_t src_ld, int rows, int cols, int n_rows, int n_cols, bool vec, int tid, int nthreads) {
+    if (vec) {
+        const int c4 = cols >> 2;
+        for (int i = tid; i < rows * c4; i += nthreads) {
+            const int j = i / c4, x = (i - j * c4) << 2;
+            const bool in = j < n_rows && x < n_cols;
+            cp_async16((uint32_t) __cvta_generic_to_shared(dst + j * dst_ld + x), in ? (const void *) (src + (size_t) j * src_ld + x) : (const void *) src, in ? 16u : 0u);
+        }
+    } else {
+        for (int i = tid; i < rows * cols; i += nthreads) {
+            const int j = i / cols, x = i - j * cols;
+            const bool in = j < n_rows && x < n_cols;
+            cp_async4(dst + j * dst_ld + x, in ? src + (size_t) j * src_ld + x : src, in);
+        }
+    }
+}
+__device__ __forceinline__ void async_copies_done() {
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
 // grid (H, chunks, ceil(V / 128)), 256 threads: thread (ty, tx) owns 8 x 8 of a 128 x 128 tile of U_c; keys and decay-scaled values
 // of the chunk are staged in shared memory
 __global__ void __launch_bounds__(256) k_retention_chunk_kv(const float * __restrict__ P, int ldp, int k_off, int v_off, const float * __restrict__ decay,
@@ -188,18 +210,16 @@ __global__ void __launch_bounds__(256) k_retention_chunk_kv(const float * __rest
     __shared__ __align__(16) float Ks[RC][128], Vs[RC][128];
     const int h = blockIdx.x, c = blockIdx.y, v0 = blockIdx.z * 128, tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int t0 = c * RC, nt = min(RC, T - t0), nch = gridDim.y;
+    __shared__ float pw[RC];
     const float g = decay[h];
-    for (int i = tid; i < RC * 128; i += 256) {
-        const int j = i >> 7, v = v0 + (i & 127);
-        Vs[j][i & 127] = (j < nt && v < V) ? P[(size_t) (t0 + j) * ldp + v_off + (size_t) h * V + v] * powf(g, (float) (nt - 1 - j)) : 0.f;
-    }
+    const bool vec = ((ldp | k_off | v_off | D | V) & 3) == 0;
+    if (tid < RC) pw[tid] = tid < nt ? powf(g, (float) (nt - 1 - tid)) : 0.f;
+    stage_tile_async(&Vs[0][0], 128, P + (size_t) t0 * ldp + v_off + (size_t) h * V + v0, (size_t) ldp, RC, 128, nt, V - v0, vec, tid, 256);
     float * U = SB + ((size_t) h * nch + c) * D * V;
     for (int d0 = 0; d0 < D; d0 += 128) {
         __syncthreads();
-        for (int i = tid; i < RC * 128; i += 256) {
-            const int j = i >> 7, d = d0 + (i & 127);
-            Ks[j][i & 127] = (j < nt && d < D) ? P[(size_t) (t0 + j) * ldp + k_off + (size_t) h * D + d] : 0.f;
-        }
+        stage_tile_async(&Ks[0][0], 128, P + (size_t) t0 * ldp + k_off + (size_t) h * D + d0, (size_t) ldp, RC, 128, nt, D - d0, vec, tid, 256);
+        async_copies_done();
         __syncthreads();
         float acc[8][8];
 #pragma unroll
@@ -210,7 +230,8 @@ __global__ void __launch_bounds__(256) k_retention_chunk_kv(const float * __rest
         for (int j = 0; j < RC; j++) {
             const float4 ka = *reinterpret_cast<const float4 *>(&Ks[j][ty * 8]), kb = *reinterpret_cast<const float4 *>(&Ks[j][ty * 8 + 4]);
             const float4 va = *reinterpret_cast<const float4 *>(&Vs[j][tx * 8]), vb = *reinterpret_cast<const float4 *>(&Vs[j][tx * 8 + 4]);
-            const float kk[8] = { ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w }, vv[8] = { va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w };
+            const float f = pw[j];                      // the key's decay until the chunk's end
+            const float kk[8] = { ka.x * f, ka.y * f, ka.z * f, ka.w * f, kb.x * f, kb.y * f, kb.z * f, kb.w * f }, vv[8] = { va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w };
 #pragma unroll
             for (int a = 0; a < 8; a++)
 #pragma unroll
@@ -247,37 +268,44 @@ __global__ void k_retention_chunk_state(const float * __restrict__ decay, int T,
     S[(size_t) h * n + e] = s;
 }
 // grid (H, chunks, ceil(V / 128)), 128 threads: warp w owns tokens 8 w .. 8 w + 7 of the chunk, a lane four value channels.
-// Dynamic shared memory: q and k of the chunk [RC][D + 4] each, the masked scores [RC][RC + 1], the values [RC][128], the powers of g.
+// Dynamic shared memory: q and k of the chunk [RC][D + 4] each, the masked scores [RC][RC + 4], the values [RC][128], the powers of g.
 __global__ void __launch_bounds__(128) k_retention_chunk_out(const float * __restrict__ P, int ldp, int q_off, int k_off, int v_off, const float * __restrict__ decay,
                                                              int T, int H, int D, int V, const float * __restrict__ SB, float * __restrict__ O) {
     extern __shared__ __align__(16) float csm[];
     const int Dp = D + 4;
-    float * Qs = csm, * Ks = Qs + RC * Dp, * As = Ks + RC * Dp, * Vs = As + RC * (RC + 1), * pw = Vs + RC * 128;
+    constexpr int AP = RC + 4;                         // score rows padded to whole 16-byte chunks
+    float * Qs = csm, * Ks = Qs + RC * Dp, * As = Ks + RC * Dp, * Vs = As + RC * AP, * pw = Vs + RC * 128;
     const int h = blockIdx.x, c = blockIdx.y, v0 = blockIdx.z * 128, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int t0 = c * RC, nt = min(RC, T - t0), nch = gridDim.y;
     const float g = decay[h];
-    for (int i = tid; i < RC * D; i += 128) {
-        const int j = i / D, d = i - j * D;
-        const float * p = P + (size_t) (t0 + (j < nt ? j : 0)) * ldp + (size_t) h * D + d;
-        Qs[j * Dp + d] = j < nt ? p[q_off] : 0.f;
-        Ks[j * Dp + d] = j < nt ? p[k_off] : 0.f;
+    {
+        const bool al = ((ldp | q_off | k_off | v_off | D | V) & 3) == 0;
+        const float * row0 = P + (size_t) t0 * ldp + (size_t) h * D;
+        stage_tile_async(Qs, Dp, row0 + q_off, (size_t) ldp, RC, D, nt, D, al, tid, 128);
+        stage_tile_async(Ks, Dp, row0 + k_off, (size_t) ldp, RC, D, nt, D, al, tid, 128);
+        stage_tile_async(Vs, 128, P + (size_t) t0 * ldp + v_off + (size_t) h * V + v0, (size_t) ldp, RC, 128, nt, V - v0, al, tid, 128);
+        if (tid <= RC) pw[tid] = powf(g, (float) tid);
+        async_copies_done();
     }
-    for (int i = tid; i < RC * 128; i += 128) {
-        const int j = i >> 7, v = v0 + (i & 127);
-        Vs[i] = (j < nt && v < V) ? P[(size_t) (t0 + j) * ldp + v_off + (size_t) h * V + v] : 0.f;
-    }
-    if (tid <= RC) pw[tid] = powf(g, (float) tid);
     __syncthreads();
-    {   // scores of the chunk against itself: thread -> token t = tid / 4, keys j = (tid % 4) * 8 .. + 7
-        const int t = tid >> 2, j0 = (tid & 3) * 8;
+    const int D4 = (D & 3) ? 0 : D;                    // 16-byte reads along d need whole chunks per row (D + 4 is then a multiple of 4 too)
+    {   // scores of the chunk against itself: lane = key j, the warp's 8 tokens; 16-byte reads along d (a lane's own key row, the
+        // tokens' query rows as broadcasts) when D is a multiple of 4, else entry by entry
         float sc[8] = { 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f };
-        for (int d = 0; d < D; d++) {
-            const float qv = Qs[t * Dp + d];
+        const float * kr = Ks + lane * Dp;
+        for (int d = 0; d < D4; d += 4) {
+            const float4 k4 = *reinterpret_cast<const float4 *>(kr + d);
 #pragma unroll
-            for (int i = 0; i < 8; i++) sc[i] = fmaf(qv, Ks[(j0 + i) * Dp + d], sc[i]);
+            for (int a = 0; a < 8; a++) {
+                const float4 q4 = *reinterpret_cast<const float4 *>(Qs + (warp * 8 + a) * Dp + d);
+                sc[a] = fmaf(q4.x, k4.x, fmaf(q4.y, k4.y, fmaf(q4.z, k4.z, fmaf(q4.w, k4.w, sc[a]))));
+            }
         }
+        for (int d = D4; d < D; d++)
 #pragma unroll
-        for (int i = 0; i < 8; i++) { const int j = j0 + i; As[t * (RC + 1) + j] = j <= t ? sc[i] * pw[t - j] : 0.f; }
+            for (int a = 0; a < 8; a++) sc[a] = fmaf(Qs[(warp * 8 + a) * Dp + d], kr[d], sc[a]);
+#pragma unroll
+        for (int a = 0; a < 8; a++) { const int t = warp * 8 + a; As[t * AP + lane] = lane <= t ? sc[a] * pw[t - lane] : 0.f; }
     }
     __syncthreads();
     float acc[8][4];
@@ -288,14 +316,28 @@ __global__ void __launch_bounds__(128) k_retention_chunk_out(const float * __res
     const float * Sc = SB + ((size_t) h * nch + c) * D * V;
     const int v = v0 + lane * 4;
     const bool vec = (V & 3) == 0 && v + 3 < V;
-#pragma unroll 4
-    for (int d = 0; d < D; d++) {
-        float sv[4];
+    const auto srow = [&](int d, float (&sv)[4]) {
         if (vec) { const float4 f = __ldg(reinterpret_cast<const float4 *>(Sc + (size_t) d * V + v)); sv[0] = f.x; sv[1] = f.y; sv[2] = f.z; sv[3] = f.w; }
         else {
 #pragma unroll
             for (int b = 0; b < 4; b++) sv[b] = v + b < V ? __ldg(Sc + (size_t) d * V + v + b) : 0.f;
         }
+    };
+#pragma unroll 2
+    for (int d = 0; d < D4; d += 4) {                   // four rows of the chunk's entry state per step, the queries as 16-byte broadcasts
+        float sv[4][4];
+#pragma unroll
+        for (int r = 0; r < 4; r++) srow(d + r, sv[r]);
+#pragma unroll
+        for (int a = 0; a < 8; a++) {
+            const float4 q4 = *reinterpret_cast<const float4 *>(Qs + (warp * 8 + a) * Dp + d);
+#pragma unroll
+            for (int b = 0; b < 4; b++) acc[a][b] = fmaf(q4.x, sv[0][b], fmaf(q4.y, sv[1][b], fmaf(q4.z, sv[2][b], fmaf(q4.w, sv[3][b], acc[a][b]))));
+        }
+    }
+    for (int d = D4; d < D; d++) {
+        float sv[4];
+        srow(d, sv);
 #pragma unroll
         for (int a = 0; a < 8; a++) {
             const float qv = Qs[(warp * 8 + a) * Dp + d];
@@ -309,12 +351,17 @@ __global__ void __launch_bounds__(128) k_retention_chunk_out(const float * __res
 #pragma unroll
         for (int b = 0; b < 4; b++) acc[a][b] *= f;
     }
-    for (int j = 0; j < RC; j++) {
-        const float4 f = *reinterpret_cast<const float4 *>(Vs + j * 128 + lane * 4);
+    for (int j = 0; j < RC; j += 4) {
+        float4 f[4];
+#pragma unroll
+        for (int r = 0; r < 4; r++) f[r] = *reinterpret_cast<const float4 *>(Vs + (j + r) * 128 + lane * 4);
 #pragma unroll
         for (int a = 0; a < 8; a++) {
-            const float w = As[(warp * 8 + a) * (RC + 1) + j];
-            acc[a][0] = fmaf(w, f.x, acc[a][0]); acc[a][1] = fmaf(w, f.y, acc[a][1]); acc[a][2] = fmaf(w, f.z, acc[a][2]); acc[a][3] = fmaf(w, f.w, acc[a][3]);
+            const float4 w = *reinterpret_cast<const float4 *>(As + (warp * 8 + a) * AP + j);
+            acc[a][0] = fmaf(w.x, f[0].x, fmaf(w.y, f[1].x, fmaf(w.z, f[2].x, fmaf(w.w, f[3].x, acc[a][0]))));
+            acc[a][1] = fmaf(w.x, f[0].y, fmaf(w.y, f[1].y, fmaf(w.z, f[2].y, fmaf(w.w, f[3].y, acc[a][1]))));
+            acc[a][2] = fmaf(w.x, f[0].z, fmaf(w.y, f[1].z, fmaf(w.z, f[2].z, fmaf(w.w, f[3].z, acc[a][2]))));
+            acc[a][3] = fmaf(w.x, f[0].w, fmaf(w.y, f[1].w, fmaf(w.z, f[2].w, fmaf(w.w, f[3].w, acc[a][3]))));
         }
     }
 #pragma unroll
