@@ -226,6 +226,20 @@ def test_far_tokens_through_the_retention_state(tmp_path):
     p.close()
 
 
+def test_long_portions_run_the_retention_chunk_by_chunk(tmp_path):
+    """portions of 128 tokens and more take the chunked form of the recurrence (32-token chunks, ragged last chunk), shorter ones
+    the token walk: both against the oracle, with head sizes that are no multiple of 4, more than 128 value channels (two column
+    tiles) and a decay so fast that its powers vanish within a chunk"""
+    layers = [retention(heads=2, dim=6, vdim=130, rot=4, decay=[0.05, 0.999]), retention(heads=3, dim=64, vdim=8, rot=64, decay=[0.9, 0.5, 0.99], mlp=moe()),
+              parallel(right=ret_mixer(heads=1, dim=9, vdim=5, rot=8, decay=[0.97]))]
+    p = Pair(tmp_path, config(layers), seed=4, n_ctx=420)
+    toks = p.tokens(400, seed=8)
+    want = p.expected(toks)
+    for cuts in (None, [128, 129, 143], [127, 1, 160, 112], [131, 5, 264], [200, 1]):
+        assert err(p.run(toks, cuts), want) < TOL32, cuts
+    p.close()
+
+
 def test_query_temperature_steps_at_multiples_of_every(tmp_path):
     """the temperature changes exactly where (p + 1) / every crosses an integer: an oracle whose step is one position off differs
     there and only there"""
