@@ -11,7 +11,7 @@
 namespace b200 {
 namespace stk {
 
-// ---- dynamic tanh: y = tanh(alpha x) w + b, element by element (no mean, no variance) -----------------------------------------
+// ---- dynamic tanh: y = tanh(alpha x) w + b, element by element: no statistic of the row enters -----------------------------------------
 struct DytW { const float * w; const float * b; float alpha; };
 __device__ __forceinline__ float dytf_(float x, const DytW & n, int i) { return fmaf(tanhf(n.alpha * x), n.w[i], n.b[i]); }
 
@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(256) k_join(const JoinArgs a) {
     }
 }
 
-// ---- retention: S <- decay_h S + k v^T, o = S^T q per head; no soft-max, no denominator --------------------------------------------
+// ---- retention: S <- decay_h S + k v^T, o = S^T q per head: a plain decayed sum, nothing divides the read-out --------------------------------------
 // P[t] = [ q: H x D | k: H x D | v: H x V | output-gate pre-activation: H x V ].
 // Step 1, per token, in place: the first rope.dims entries of every q and k head are rotated by the token's position
 // ('rotate half' pairs), then k is scaled by k_scale (D^(-1/2)). grid (T, ceil(2 H / warps per block)): a warp per head.
@@ -441,7 +441,7 @@ __global__ void __launch_bounds__(512) k_retention_token(const float * __restric
 
 // ---- sigmoid attention over grouped key/value heads -------------------------------------------------------------------------------
 // P[t] = [ q: H x D | k: G x D | v: G x V ]. Query head h reads key/value head h / (H / G); position p sees every j <= p.
-// The weight of key j for head h is sigmoid((q . k_j) scale - slope[h] (p - j) + pb[h]); weights are not normalised over keys.
+// The weight of key j for head h is sigmoid((q . k_j) scale - slope[h] (p - j) + pb[h]); a row's weights are used as they are (they need not sum to one).
 // Step 1, per token: q and k are each divided by the root mean square of their WHOLE projection (all heads at once, eps inside
 // the root) and multiplied by plain weights; q is also multiplied by the position's temperature
 // 1 + coef ln(floor((p + 1) / every) + 1); every value head is divided by its own root mean square (no weight). Queries go to
@@ -615,9 +615,9 @@ __global__ void k_group_o_layout(const float * __restrict__ Or, int Tpad, int H,
 }
 
 // ---- routed mixture of gated units --------------------------------------------------------------------------------------------------
-// Router, per token, in float32: z = W_r h, s = softmax(z) over all n experts. The experts form n_groups equal groups of
-// neighbours; a group's score is its largest s; only experts of the `keep` best groups are eligible; the `top` eligible experts
-// with the largest s are chosen (lowest index first among equals) with weights s * scale, not renormalised.
+// Router, per token, in float32: z = W_r h, s = softmax(z) over all n experts. The expert list is cut into n_groups consecutive blocks
+// of equal size; a block ranks by the best s inside it and the choice is confined to the `keep` best-ranked blocks: of their experts
+// the `top` with the largest s are taken (lowest index first among equals), each weighing in with s * scale as it is.
 // sel[t][top], wt[t][top]; sg[t] = sigmoid(w_sg . h) is the shared unit's gate (w_sg == nullptr: no shared unit).
 // grid (T, ceil(rows / 8)) with rows = n (+ 1 for the shared gate): a warp per row of the router, several 16-byte loads in flight;
 // the logits go to z[t][n + 1], and the block of a token that finishes last (an atomic counter, no waiting) makes the choice with

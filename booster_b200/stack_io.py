@@ -59,7 +59,7 @@ def tosevik_config(width: int, n_layer: int, ff: int, heads: int, vocab: int = 3
     """a Tosevik configuration whose layers resemble a real model's: mixers in `pattern` order, a routed mixture on every layer whose
     chosen experts plus the shared unit are as wide together as a dense feed-forward of `ff` (top x 3 ff / 16 + ff / 4)"""
     def ret(h, dim, vdim):
-        return {"heads": h, "dim": dim, "vdim": vdim, "rot": {"base": 1000000.0, "dims": dim // 2},
+        return {"heads": h, "dim": dim, "vdim": vdim, "rot": {"base": 500000.0, "dims": dim // 2},
                 "decay": [1.0 - 2.0 ** (-5.0 - 3.0 * i / h) for i in range(h)]}
     e_ff = max(8, ff * 3 // (4 * top) // 8 * 8)
     layers = []
@@ -72,7 +72,7 @@ def tosevik_config(width: int, n_layer: int, ff: int, heads: int, vocab: int = 3
                            "q_temp": {"coef": 0.1, "every": 1024}},
                   "right": ret(heads, head_dim // 2, head_dim)}
         mlp = {"kind": "moe", "expert": {"ff": e_ff}, "shared": {"ff": ff - top * e_ff},
-               "router": {"experts": experts, "top": top, "scale": 1.5, "groups": {"count": groups[0], "keep": groups[1]}}}
+               "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": groups[0], "keep": groups[1]}}}
         layers.append({"type": kind, "mixer": mx, "mlp": mlp})
     return {"architecture": "Tosevik", "layers": layers, "norm": {"eps": 1e-6}, "vocab": vocab, "width": width}
 

@@ -301,7 +301,7 @@ def random_config(rng):
     def rnd_ret():
         d = pick([2, 4, 16, 32, 48, 128])
         h = pick([1, 2, 3, 6])
-        return ret_mixer(heads=h, dim=d, vdim=pick([4, 8, 48, 128, 200]), rot=pick([r for r in (0, 2, 4, 16, 32, 48, 128) if r <= d]), base=float(rng.choice([100.0, 1e4, 1e6])),
+        return ret_mixer(heads=h, dim=d, vdim=pick([4, 8, 48, 128, 200]), rot=pick([r for r in (0, 2, 4, 16, 32, 48, 128) if r <= d]), base=float(rng.choice([100.0, 1e4, 5e5])),
                          decay=[float(x) for x in 1.0 - 2.0 ** -rng.uniform(1, 9, size=h)])
 
     def rnd_moe():

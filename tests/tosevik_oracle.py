@@ -53,7 +53,7 @@ def rotate_front(x, pos, rot):
 
 
 def mix_retention(h, W, mx, eps):
-    """S <- decay_h S + k v^T, o = S^T q per head, no soft-max and no denominator"""
+    """S <- decay_h S + k v^T, o = S^T q per head: a plain decayed sum, nothing divides the read-out"""
     T = h.shape[0]
     H, D, V = mx["heads"], mx["dim"], mx["vdim"]
     pos = np.arange(T)
@@ -103,7 +103,7 @@ def gated_unit(h, W):
 
 
 def route(h, W, r):
-    """-> chosen [T, top] expert indices and their weights: soft-max over all experts, only the best groups are eligible"""
+    """-> chosen [T, top] expert indices and their weights: soft-max over all experts, the choice confined to the best-ranked blocks of experts"""
     z = h @ W["router"].T
     e = np.exp(z - z.max(-1, keepdims=True))
     s = e / e.sum(-1, keepdims=True)
