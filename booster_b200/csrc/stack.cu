@@ -1591,13 +1591,12 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
         }
         for (const Cached & cd : cached) {
             const LayerSpec & L = *cd.L;
-            const struct { int cache_index; } R{ cd.index };
             {   // [ window - 1 zero rows | n_ctx positions | one tile of slack ]: a tile's key range may start before position 0 and end past the portion
                 const size_t front = (size_t) std::max(L.window, 1), rows = front + (size_t) n_ctx + 2 * ATT_TQ;
                 float * base = nullptr;
                 fl(&base, rows * L.cache_row);
                 c->cache_allocs.push_back(base);
-                c->caches[(size_t) R.cache_index] = base + front * L.cache_row;
+                c->caches[(size_t) cd.index] = base + front * L.cache_row;
                 const size_t nk = (L.window > 0 ? (size_t) L.window + ATT_TQ - 1 : (size_t) n_ctx + ATT_TQ) + 3;
                 const size_t one = (size_t) ATT_TQ * L.H * nk * (L.kind == MIX_DIFFATTN ? 2 : 1);     // one tile's scores (two maps per head)
                 const size_t all = (cap_t / ATT_TQ) * one;
