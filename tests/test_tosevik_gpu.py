@@ -405,6 +405,36 @@ def test_greedy_generation_through_the_bridge(tmp_path, monkeypatch):
     p.close()
 
 
+def test_trace_runner_replays_steps_and_reuses_a_finished_requests_context(tmp_path):
+    """bin/trace_run on a folder model: steps arrive as JSON lines, the wanted rows of each step come back as a float32 file, a
+    request that ends gives its context back and the next request starts from a clean one"""
+    import json
+    import os
+    import subprocess
+    import sys
+    cfg = config(FULL[:3])
+    w = to.random_model(cfg, 5)
+    d = to.write_model(str(tmp_path / "m"), cfg, w)
+    rng = np.random.default_rng(3)
+    a, b = rng.integers(0, cfg["vocab"], size=40).tolist(), rng.integers(0, cfg["vocab"], size=23).tolist()
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:31], "want": [0, 7, 30]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[31:33], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[33:40], "want": [6, 1]}], "end": ["a"]},
+             {"step": 3, "entries": [{"id": "b", "tokens": b[:22], "want": [21]}], "end": []},
+             {"step": 4, "entries": [{"id": "b", "tokens": b[22:], "want": [0]}], "end": ["b"]}]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", d, "--dtype", "float32", "--out", str(out), "--max-tokens", "64"],
+                       input="".join(json.dumps(x) + "\n" for x in steps).encode(), stdout=subprocess.PIPE, stderr=subprocess.PIPE, timeout=600)
+    assert r.returncode == 0, r.stderr.decode()[-2000:]
+    assert [l for l in r.stdout.decode().split("\n") if l.startswith("done")] == ["done %d" % i for i in range(5)]
+    assert not (out / "1.f32").exists()
+    wa, wb = to.forward(cfg, w, a), to.forward(cfg, w, b)
+    for n, want in ((0, wa[[0, 7, 30]]), (2, wa[[39, 34]]), (3, wb[[21]]), (4, wb[[22]])):
+        got = np.fromfile(str(out / ("%d.f32" % n)), "<f4").reshape(len(want), cfg["vocab"])
+        assert err(got, want) < TOL32, n
+
+
 def test_bad_models_fail_loudly(tmp_path):
     cfg = config([retention(mlp=moe()), parallel()])
     w = to.random_model(cfg)
