@@ -14,7 +14,7 @@ $(OBJDIR)/engine.o: $(CSRC)/engine.cu $(CSRC)/kernels.cuh $(CSRC)/token_kernel.c
 	@mkdir -p $(OBJDIR)
 	$(NVCC) $(NVCCFLAGS) -c $< -o $@ 2> $(OBJDIR)/engine.ptxas.log || (cat $(OBJDIR)/engine.ptxas.log; false)
 
-$(OBJDIR)/stack.o: $(CSRC)/stack.cu $(CSRC)/stack_kernels.cuh $(CSRC)/stack_kernels_mix.cuh $(CSRC)/stack.hpp $(CSRC)/safetensors.hpp
+$(OBJDIR)/stack.o: $(CSRC)/stack.cu $(CSRC)/stack_kernels.cuh $(CSRC)/stack_kernels_mix.cuh $(CSRC)/stack_kernels_hyper.cuh $(CSRC)/stack.hpp $(CSRC)/safetensors.hpp
 	@mkdir -p $(OBJDIR)
 	$(NVCC) $(NVCCFLAGS) -c $< -o $@ 2> $(OBJDIR)/stack.ptxas.log || (cat $(OBJDIR)/stack.ptxas.log; false)
 

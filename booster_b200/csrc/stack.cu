@@ -14,11 +14,19 @@
 //              the embedding output and all layers' results so far; mixers retention | parallel (sigmoid attention with a distance
 //              penalty beside a retention, each normed, averaged); routed mixture of gated units with group-limited choice and a
 //              gated shared unit
+//   Rumurax    the residual is several streams; every sub-layer reads their weighted sum through an RMS norm whose weight is one
+//              number and writes all streams at once through a mixing matrix (hyper-connections). Mixers: soft-max attention
+//              over grouped heads with normed queries and keys, under a chunk mask (score cap, logarithmic distance penalty,
+//              sink, per-head gate) or under a sliding window that also sees means of whole blocks of older cached keys and
+//              values (rotation of neighbouring pairs); both may mix their values with the first such layer's | latent
+//              attention (causal, gated entry by entry). Routed mixture: sigmoid scores, experts run on the weighted input,
+//              an ungated shared unit
 // A model is executed as a list of layer RUNS: (layer, state slot), one per layer unless the design repeats some.
 #include "stack.hpp"
 #include "safetensors.hpp"
 #include "stack_kernels.cuh"
 #include "stack_kernels_mix.cuh"
+#include "stack_kernels_hyper.cuh"
 
 #include <algorithm>
 #include <cmath>
@@ -36,8 +44,8 @@ using namespace stk;
 
 namespace {
 
-enum MixerKind { MIX_MINGRU = 0, MIX_LATENT, MIX_DELTA, MIX_GDELTA, MIX_DIFFATTN, MIX_RETENTION, MIX_SIGATTN, MIX_PAIR };
-enum BlockKind { BLOCK_SEQUENTIAL = 0, BLOCK_PARALLEL, BLOCK_PRENORM };
+enum MixerKind { MIX_MINGRU = 0, MIX_LATENT, MIX_DELTA, MIX_GDELTA, MIX_DIFFATTN, MIX_RETENTION, MIX_SIGATTN, MIX_PAIR, MIX_GQATTN };
+enum BlockKind { BLOCK_SEQUENTIAL = 0, BLOCK_PARALLEL, BLOCK_PRENORM, BLOCK_HYPER };
 enum FfKind { FF_GLU = 0, FF_POLY, FF_MOE };
 constexpr int CHUNK_MAX = 512;          // tokens per pass of a prompt portion (longer steps run as several passes)
 constexpr float GLU_ALPHA = 1.702f;     // the feed-forward's sigmoid slope: fixed by the design
@@ -67,6 +75,8 @@ struct LayerSpec {
     DMat uq;                             // query latent -> H x D
     float * qnorm = nullptr;
     bool head_gate = false;
+    int gate_rows = 0;                   // rows of the gate projection: H (one number per head) or H x V (one per entry)
+    bool rope_adjacent = false;          // rotation pairs are neighbours (2i, 2i + 1) instead of (i, i + dims / 2)
     // gated delta rule
     int KH = 0, taps = 0;
     DMat proj;                           // q | k | v | beta | decay | gate stacked
@@ -84,6 +94,8 @@ struct LayerSpec {
     // FF_MOE: routed mixture of gated units. e_gateup [n_exp][2 e_ff][E] (gate / up interleaved), e_down [n_exp][E][e_ff]
     int n_exp = 0, top = 0, n_groups = 1, keep_groups = 1, e_ff = 0;
     float r_scale = 1.f;
+    int route_fn = 0;                    // 0: soft-max over the experts; 1: sigmoid of each logit
+    bool scale_input = false;            // the choice's weight multiplies the expert's input instead of its output
     float * router = nullptr, * w_sg = nullptr;      // float32: the router is computed in 32-bit
     DMat e_gateup, e_down;
     // element-wise norms (dynamic tanh): weight in norm1 / norm2, bias and slope here
@@ -99,6 +111,16 @@ struct LayerSpec {
     float * qw = nullptr, * kw = nullptr, * pb = nullptr, * slope = nullptr;
     float t_coef = 0.f;
     int t_every = 0;
+    // soft-max attention over grouped heads (MIX_GQATTN): proj = q | k | v | head gates; window = the mask's size; qw / kw are the
+    // per-head norm weights [D]
+    int mask_kind = 0, pool = 0;         // MASK_*; pool > 0: means of whole blocks of `pool` cached rows stand in for what lies before the window
+    float cap = 0.f;                     // > 0: score <- cap tanh(score / cap)
+    float * r1 = nullptr, * r2 = nullptr;
+    int vmode = 0;                       // GQA_V_*: values left for later layers / mixed with the first mixing layer's
+    float vlambda = 0.f;
+    // hyper-connections (BLOCK_HYPER): the weights of both sub-layers, and norm weights that are one number
+    HcW hc[2];
+    float g1 = 1.f, g2 = 1.f;
     // a pair of mixers side by side (MIX_PAIR): each over its root mean square times a weight, then their mean
     std::vector<LayerSpec> parts;
     float * pair_w[2] = { nullptr, nullptr };
@@ -132,6 +154,9 @@ struct StackModel {
     float embed_alpha = 1.f, final_alpha = 1.f;
     bool depth_avg = false;               // every layer hands on a weighted sum of all results so far
     bool has_pair = false;
+    int streams = 1;                      // BLOCK_HYPER: copies of the residual
+    bool rope_adjacent = false;           // the design rotates neighbouring pairs
+    int vfirst_width = 0;                 // key/value heads x vdim of the first value-mixing layer (0: none so far)
     int max_slots = 0, max_eff = 0, max_exp = 0;      // routed mixtures: choices per token, expert width, experts
     size_t max_ret_state = 0;             // retention: the largest heads x dim x vdim
     int max_ret_dim = 0;
@@ -160,6 +185,8 @@ struct StackCtx {
     StackModel * m = nullptr;
     int n_ctx = 0, n_past = 0, cap = 0;
     cudaStream_t st = nullptr;
+    float * XS = nullptr, * VF = nullptr; // hyper-connections: the streams [S][cap][E]; value mixing: the first mixing layer's values of this pass [cap][G V]
+    std::vector<float *> pools;           // per attention cache: means of whole blocks of cached rows (nullptr: the layer keeps none)
     float * Y2 = nullptr, * U = nullptr, * XC = nullptr;     // parallel blocks: the feed-forward's output, the convolved inputs [2][cap][E], [x; x0] rows
     const float * in = nullptr;           // what the mixer being enqueued reads ([T][E]) ...
     float * out = nullptr;                // ... and writes
@@ -272,21 +299,27 @@ void load_latent(StackModel & m, LayerSpec & L, const Json & mx, const safetenso
     if (L.window < 0) throw std::runtime_error("config: mask.size must not be negative");
     const int qr = L.q_rank = (int) mx.integer("q_rank", 0);
     if (qr < 0) throw std::runtime_error("config: q_rank must not be negative");
-    L.head_gate = sf.find(p + "g") != nullptr;
+    if (const st_tensor * gt = sf.find(p + "g")) {
+        // one gate per head ([H][E]) or one per entry of the concatenated heads ([H V][E])
+        if (gt->shape.size() != 2 || (gt->shape[0] != H && gt->shape[0] != (int64_t) H * V)) throw std::runtime_error("tensor '" + p + "g' must have heads or heads x vdim rows");
+        L.head_gate = true;
+        L.gate_rows = (int) gt->shape[0];
+    }
+    L.rope_adjacent = m.rope_adjacent;
     if (qr > 0) {
         // queries through a latent: [ W_dq | W_dkv | W_g ] in one product, then norm and W_uq
         if (R) throw std::runtime_error("latent attention: a query latent with a rotated part is not implemented");
         std::vector<float> W = sf.read_f32(p + "dq", {qr, E});
         append(W, sf.read_f32(p + "dkv", {rank, E}));
-        if (L.head_gate) append(W, sf.read_f32(p + "g", {H, E}));
-        L.qdkv = up_mat(m, W, qr + rank + (L.head_gate ? H : 0), E, nullptr);
+        if (L.head_gate) append(W, sf.read_f32(p + "g", {L.gate_rows, E}));
+        L.qdkv = up_mat(m, W, qr + rank + L.gate_rows, E, nullptr);
         L.qnorm = up_f32(m, sf.read_f32(p + "dq.norm", {qr}));
         L.uq = up_mat(m, sf.read_f32(p + "uq", {H * D, qr}), H * D, qr, nullptr);
     } else {
         std::vector<float> W = sf.read_f32(p + "q", {H * (D + R), E});
         append(W, sf.read_f32(p + "dkv", {rank + R, E}));
-        if (L.head_gate) append(W, sf.read_f32(p + "g", {H, E}));
-        L.qdkv = up_mat(m, W, H * (D + R) + rank + R + (L.head_gate ? H : 0), E, nullptr);
+        if (L.head_gate) append(W, sf.read_f32(p + "g", {L.gate_rows, E}));
+        L.qdkv = up_mat(m, W, H * (D + R) + rank + R + L.gate_rows, E, nullptr);
     }
     L.cnorm = up_f32(m, sf.read_f32(p + "dkv.norm", {rank}));
     // W_uk [H*D][rank] -> per head transposed [rank][D]: the unrotated score q_h . (W_uk,h c) = (W_uk,h^T q_h) . c
@@ -490,6 +523,54 @@ void load_sigattn(StackModel & m, LayerSpec & L, const Json & mx, const safetens
     m.maxQK = std::max(m.maxQK, H * D); m.maxOL = std::max(m.maxOL, H * V);
 }
 
+float read_scalar(const safetensors_file & sf, const std::string & name);
+// soft-max attention over grouped heads: '<prefix>{q,k,v,o}', optional 'q.norm' / 'k.norm' [dim], 'r1' / 'r2' [heads] (distance
+// penalty), 'sink' [heads], 'g' [heads][E] (output gate), 'vmix' (one number). Configuration: heads, kv_heads, dim, vdim, scale,
+// softcap, rot.{base,dims}, mask.{size,pool}, v_mix. The mask's kind belongs to the mixer's name (chunks | window).
+void load_gqattn(StackModel & m, LayerSpec & L, const Json & mx, const safetensors_file & sf, const std::string & p, int mask_kind) {
+    const int E = m.E;
+    const int H = L.H = need_int(mx, "heads"), G = L.KH = (int) mx.integer("kv_heads", H), D = L.D = need_int(mx, "dim"), V = L.V = need_int(mx, "vdim");
+    if (G < 1 || H % G) throw std::runtime_error("config: attention heads must be a multiple of kv_heads");
+    if (V > 256) throw std::runtime_error("attention: vdim above 256 is not supported by the attention kernel");
+    L.scale = (float) mx.number("scale");
+    L.cap = (float) mx.number("softcap", 0.0);
+    if (L.cap < 0.f) throw std::runtime_error("config: softcap must not be negative");
+    L.mask_kind = MASK_CAUSAL; L.window = 0; L.pool = 0;
+    if (mx.has("mask")) {
+        L.mask_kind = mask_kind;
+        L.window = need_int(mx.at("mask"), "size");
+        if (mask_kind == MASK_WINDOW) L.pool = (int) mx.at("mask").integer("pool", 0);
+        if (L.pool < 0) throw std::runtime_error("config: mask.pool must not be negative");
+    }
+    load_rot(m, L, mx, D);
+    L.rope_adjacent = m.rope_adjacent;
+    std::vector<float> W = sf.read_f32(p + "q", {H * D, E});
+    append(W, sf.read_f32(p + "k", {G * D, E}));
+    append(W, sf.read_f32(p + "v", {G * V, E}));
+    if (sf.find(p + "g")) { append(W, sf.read_f32(p + "g", {H, E})); L.head_gate = true; L.gate_rows = H; }
+    L.proj = up_mat(m, W, H * D + G * D + G * V + L.gate_rows, E, nullptr);
+    if (sf.find(p + "q.norm")) L.qw = up_f32(m, sf.read_f32(p + "q.norm", {D}));
+    if (sf.find(p + "k.norm")) L.kw = up_f32(m, sf.read_f32(p + "k.norm", {D}));
+    if (sf.find(p + "r1")) { L.r1 = up_f32(m, sf.read_f32(p + "r1", {H})); L.r2 = up_f32(m, sf.read_f32(p + "r2", {H})); }
+    if (sf.find(p + "sink")) L.sink = up_f32(m, sf.read_f32(p + "sink", {H}));
+    L.vmode = GQA_V_PLAIN;
+    if (mx.has("v_mix") && mx.at("v_mix").kind == Json::Bool && mx.at("v_mix").b) {
+        if (m.vfirst_width == 0) { L.vmode = GQA_V_FIRST; m.vfirst_width = G * V; }      // the first mixing layer's own weight is unused
+        else {
+            if (m.vfirst_width != G * V) throw std::runtime_error("config: value-mixing layers must agree in kv_heads x vdim");
+            L.vmode = GQA_V_MIX;
+            L.vlambda = read_scalar(sf, p + "vmix");
+        }
+    }
+    L.o = up_mat(m, sf.read_f32(p + "o", {E, H * V}), E, H * V, nullptr);
+    L.cache_row = (size_t) G * D + (size_t) G * V;
+    m.maxP = std::max(m.maxP, L.proj.N); m.maxA = std::max(m.maxA, H * V);
+    m.maxCV = std::max(m.maxCV, H * D);
+    m.maxQK = std::max(m.maxQK, H * D); m.maxOL = std::max(m.maxOL, H * V);
+}
+void load_gqattn_chunks(StackModel & m, LayerSpec & L, const Json & mx, const safetensors_file & sf, const std::string & p) { load_gqattn(m, L, mx, sf, p, MASK_CHUNK); }
+void load_gqattn_window(StackModel & m, LayerSpec & L, const Json & mx, const safetensors_file & sf, const std::string & p) { load_gqattn(m, L, mx, sf, p, MASK_WINDOW); }
+
 struct MixerEntry;
 const MixerEntry & find_mixer(const std::string & type, size_t layer);
 void load_pair(StackModel & m, LayerSpec & L, const Json & mx, const safetensors_file & sf, const std::string & p);
@@ -504,6 +585,8 @@ const MixerEntry MIXERS[] = {
     { "retention", MIX_RETENTION, load_retention },
     { "sigmoid_attention", MIX_SIGATTN, load_sigattn },
     { "parallel", MIX_PAIR, load_pair },
+    { "chunk_attention", MIX_GQATTN, load_gqattn_chunks },
+    { "window_attention", MIX_GQATTN, load_gqattn_window },
 };
 
 const MixerEntry & find_mixer(const std::string & type, size_t layer) {
@@ -704,8 +787,11 @@ DMat load_glu_pair(StackModel & m, const safetensors_file & sf, const std::strin
     if (into) { append(*into, W); return DMat(); }
     return up_mat(m, W, 2 * ff, E, nullptr);
 }
-void load_mixture(StackModel & m, LayerSpec & L, const Json & mj, const safetensors_file & sf, const std::string & p) {
+// what a design fixes about its routed mixture: the score function, where a choice's weight is applied, a gate on the shared unit
+struct MixtureKind { int route_fn; bool scale_input; bool shared_gate; };
+void load_mixture(StackModel & m, LayerSpec & L, const Json & mj, const safetensors_file & sf, const std::string & p, const MixtureKind & mk) {
     const int E = m.E;
+    L.route_fn = mk.route_fn; L.scale_input = mk.scale_input;
     const Json & rj = mj.at("router");
     const int n = L.n_exp = need_int(rj, "experts"), top = L.top = need_int(rj, "top");
     L.r_scale = (float) rj.number("scale", 1.0);
@@ -733,7 +819,7 @@ void load_mixture(StackModel & m, LayerSpec & L, const Json & mj, const safetens
         const int sff = L.ff = need_int(mj.at("shared"), "ff");
         L.gateup = load_glu_pair(m, sf, p + "shared.", sff, E, nullptr);
         L.down = up_mat(m, sf.read_f32(p + "shared.down", {E, sff}), E, sff, nullptr);
-        L.w_sg = up_f32(m, sf.read_f32(p + "shared.sg", {1, E}));
+        if (mk.shared_gate) L.w_sg = up_f32(m, sf.read_f32(p + "shared.sg", {1, E}));
         m.maxA = std::max(m.maxA, sff);
     }
     m.max_slots = std::max(m.max_slots, top); m.max_eff = std::max(m.max_eff, ff); m.max_exp = std::max(m.max_exp, n);
@@ -771,7 +857,7 @@ void build_tosevik(StackModel & m, const Json & cfg, const safetensors_file & sf
             const std::string kind = mj.string("kind", "moe");
             if (kind != "moe") throw std::runtime_error("config: feed-forward kind '" + kind + "' is not part of the Tosevik design (moe)");
             L.norm2 = up_f32(m, sf.read_f32(p + "norm2", {E})); L.n2_b = up_f32(m, sf.read_f32(p + "norm2.b", {E})); L.n2_alpha = read_scalar(sf, p + "norm2.alpha");
-            load_mixture(m, L, mj, sf, p + "mlp.");
+            load_mixture(m, L, mj, sf, p + "mlp.", MixtureKind{0, false, true});
         }
         L.n_dwa = i + 2;
         L.dwa = up_f32(m, sf.read_f32(p + "dwa", {i + 2}));
@@ -784,11 +870,77 @@ void build_tosevik(StackModel & m, const Json & cfg, const safetensors_file & sf
     m.head = up_mat(m, sf.read_f32("head", {m.vocab, E}), m.vocab, E, nullptr);
 }
 
+// Rumurax: embed -> S equal streams -> layers (per sub-layer: u = sum_s in[s] x_s; y = f(norm(u) g); x_t <- sum_s mix[s][t] x_s +
+// out[t] y, tensors '<layer>.hc1.*' for the mixer and '<layer>.hc2.*' for the mixture) -> sum of the streams -> norm -> head.
+// Norm weights are one number each. The design's mixer names map to registry entries; rotations pair neighbours.
+HcW load_hc(const safetensors_file & sf, const std::string & p, int S) {
+    HcW w{};
+    if (!sf.find(p + "in")) {
+        if (S != 1) throw std::runtime_error("tensor '" + p + "in' is missing");
+        w.in[0] = w.mix[0] = w.out[0] = 1.f;                 // one stream and no weights: the plain residual sum
+        return w;
+    }
+    const std::vector<float> a = sf.read_f32(p + "in", {S}), b = sf.read_f32(p + "out", {S}), M = sf.read_f32(p + "mix", {S, S});
+    for (int i = 0; i < S; i++) { w.in[i] = a[(size_t) i]; w.out[i] = b[(size_t) i]; }
+    for (int i = 0; i < S * S; i++) w.mix[i] = M[(size_t) i];      // [from][to]
+    return w;
+}
+void build_rumurax(StackModel & m, const Json & cfg, const safetensors_file & sf) {
+    static const char * const alias[][2] = { { "attention", "chunk_attention" }, { "attention_2", "window_attention" }, { "latent_attention", "latent_attention" } };
+    m.block = BLOCK_HYPER;
+    m.rope_adjacent = true;
+    m.vocab = need_int(cfg, "vocab"); m.E = need_int(cfg, "width");
+    m.eps = (float) cfg.at("norm").number("eps");
+    m.groups = 1;
+    const int S = m.streams = (int) cfg.integer("streams", 1);
+    if (S < 1 || S > HC_MAX) throw std::runtime_error("config: 'streams' must lie between 1 and " + std::to_string(HC_MAX));
+    const int E = m.E;
+    {
+        DMat d = up_mat(m, sf.read_f32("embed", {m.vocab, E}), m.vocab, E, nullptr);
+        m.embed = d.w;
+        m.weight_bytes -= d.bytes;
+    }
+    const Json & layers = cfg.at("layers");
+    if (layers.kind != Json::Arr || layers.arr.empty()) throw std::runtime_error("config: 'layers' must be a non-empty list");
+    const int n = (int) layers.arr.size();
+    for (int i = 0; i < n; i++) {
+        const Json & lj = layers.arr[(size_t) i];
+        const std::string type = lj.string("type", ""), p = "l" + std::to_string(i) + ".";
+        const char * entry = nullptr;
+        for (const auto & a : alias) if (type == a[0]) entry = a[1];
+        if (!entry) throw std::runtime_error("config: layer " + std::to_string(i) + ": mixer '" + type + "' is not part of the Rumurax design");
+        const MixerEntry * me = &find_mixer(entry, (size_t) i);
+        const int64_t bytes0 = m.weight_bytes;
+        m.layers.emplace_back();
+        LayerSpec & L = m.layers.back();
+        L.kind = me->kind;
+        L.has_mlp = lj.has("mlp");
+        L.g1 = read_scalar(sf, p + "norm1");
+        L.hc[0] = load_hc(sf, p + "hc1.", S);
+        me->load(m, L, lj.at("mixer"), sf, p + "mix.");
+        if (L.kind == MIX_LATENT && (L.q_rank || L.sink || L.window)) throw std::runtime_error("config: the Rumurax latent attention has no query latent, sink or window");
+        if (L.has_mlp) {
+            const Json & mj = lj.at("mlp");
+            const std::string kind = mj.string("kind", "moe");
+            if (kind != "moe") throw std::runtime_error("config: feed-forward kind '" + kind + "' is not part of the Rumurax design (moe)");
+            L.g2 = read_scalar(sf, p + "norm2");
+            L.hc[1] = load_hc(sf, p + "hc2.", S);
+            load_mixture(m, L, mj, sf, p + "mlp.", MixtureKind{1, true, false});
+        }
+        L.bytes = m.weight_bytes - bytes0;
+        m.weight_bytes = bytes0;
+        add_run(m, i, -1);
+    }
+    m.final_norm = up_f32(m, std::vector<float>((size_t) E, read_scalar(sf, "final.norm")));
+    m.head = up_mat(m, sf.read_f32("head", {m.vocab, E}), m.vocab, E, nullptr);
+}
+
 struct DesignEntry { const char * name; void (*build)(StackModel &, const Json &, const safetensors_file &); };
 const DesignEntry DESIGNS[] = {
     { "Matulorn", build_matulorn },
     { "Dopilorn", build_dopilorn },
     { "Tosevik", build_tosevik },
+    { "Rumurax", build_rumurax },
 };
 
 // ---- launches ---------------------------------------------------------------------------------------------------------
@@ -812,13 +964,14 @@ struct LinOpt {
     const int32_t * seg = nullptr;
     const int32_t * w_index = nullptr;
     int x_share = 1;
+    const float * x_scale = nullptr;        // mat-vec: entry z runs on x_scale[z] times its input row
 };
 void linear_on(cudaStream_t st, int dtype, int64_t * launches, const float * X, int ldx, const void * W, const float * bias, float * Y, int ldy,
                int T, int N, int K, int batch = 1, long long sX = 0, long long sW = 0, long long sY = 0, bool glu = false, float glu_limit = 0.f,
                const UmmaScratch * us = nullptr, const LinOpt * opt = nullptr) {
     if (T <= 0 || N <= 0) return;
     LinArgs a{X, W, bias, Y, T, N, K, ldx, ldy, sX, sW, sY, 0, glu ? 1 : 0, glu_limit, GLU_ALPHA, 0, 0};
-    if (opt) { a.alpha = opt->alpha; a.up_shift = opt->shift; a.seg = opt->seg; a.w_index = opt->w_index; a.x_share = opt->x_share; }
+    if (opt) { a.alpha = opt->alpha; a.up_shift = opt->shift; a.seg = opt->seg; a.w_index = opt->w_index; a.x_share = opt->x_share; a.x_scale = opt->x_scale; }
     const int xbatch = a.seg ? 1 : batch;      // segments: X is one matrix of T rows
     const int vecw = dtype == STACK_F32 ? 4 : 8;
     const auto al16 = [](const void * p) { return ((uintptr_t) p & 15) == 0; };
@@ -929,10 +1082,11 @@ AttnPlan plan_attention(const LayerSpec & L, int n_ctx, int T, int sm_count) {
 // float32 product on the CUDA cores with explicit operand layout (the attention's two products over cached rows)
 // A second batch level (nz2 products per first-level index, strides sX2 / sW2 / sY2) serves operands that are cut twice: tiles x heads.
 void gemm_f32(StackCtx * c, const float * X, int ldx, long long sX, const float * W, int w_kn, int ldw, long long sW, float * Y, int ldy, long long sY,
-              int M, int N, int K, int batch, int nz2 = 1, long long sX2 = 0, long long sW2 = 0, long long sY2 = 0) {
+              int M, int N, int K, int batch, int nz2 = 1, long long sX2 = 0, long long sW2 = 0, long long sY2 = 0, int accum = 0) {
     const auto al16 = [](const void * p) { return ((uintptr_t) p & 15) == 0; };
     LinArgs a{X, W, nullptr, Y, M, N, K, ldx, ldy, sX, sW, sY, 0, 0, 0.f, 0.f, w_kn, ldw, nz2, sX2, sW2, sY2};
     a.vec = K % 4 == 0 && ldx % 4 == 0 && sX % 4 == 0 && sW % 4 == 0 && sX2 % 4 == 0 && sW2 % 4 == 0 && ldw % 4 == 0 && al16(X) && al16(W);
+    a.accum = accum;
     k_gemm_simt<float><<<dim3((unsigned) ((N + 63) / 64), (unsigned) ((M + 63) / 64), (unsigned) (batch * nz2)), 256, 0, c->st>>>(a);
     c->launches++;
 }
@@ -943,7 +1097,7 @@ constexpr size_t ATT_SCORE_BYTES = (size_t) 256 << 20;
 void latent_values_out(StackCtx * c, const LayerSpec & L, int T, int ldp, int gate_off) {
     const int H = L.H, V = L.V, rank = L.rank;
     linear(c, c->OL, H * rank, L.uv, c->A, H * V, T, H, rank, V);
-    if (L.head_gate) { k_head_gate<<<T, 256, 0, c->st>>>(c->A, c->P + gate_off, ldp, H, V); c->launches++; }
+    if (L.head_gate) { k_head_gate<<<T, 256, 0, c->st>>>(c->A, c->P + gate_off, ldp, H, V, L.gate_rows == H ? 0 : 1); c->launches++; }
     linear(c, c->A, H * V, L.o, c->out, c->m->E, T);
 }
 
@@ -952,7 +1106,7 @@ void mixer_latent(StackCtx * c, const LayerSpec & L, const RunSpec & Rn, int T) 
     const int ldp = L.qdkv.N;
     float * cache = c->caches[(size_t) Rn.cache_index];
     linear(c, c->in, E, L.qdkv, c->P, ldp, T);
-    const RopeArgs rope{L.rope_freq, L.rope_dims, L.rope_mag};
+    const RopeArgs rope{L.rope_freq, L.rope_dims, L.rope_mag, L.rope_adjacent ? 1 : 0};
     int gate_off;
     if (L.q_rank > 0) {
         // P[t] = [ query latent | down-projection | head gates ]: norm of the query latent in place, q = W_uq c_q into A, cache row, absorbed queries from A
@@ -1216,6 +1370,83 @@ void mixer_sigattn(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) 
     linear(c, c->A, H * V, L.o, c->out, E, T);
 }
 
+constexpr int GQA_MAX_SPLIT = 16;
+int gqa_vpl(const LayerSpec & L) { return L.V <= 32 ? 1 : L.V <= 64 ? 2 : L.V <= 128 ? 4 : 8; }
+bool gqa_tiles_enabled() {
+    static const bool on = [] { const char * e = std::getenv("BOOSTER_B200_STACK_GQA_TILES"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
+// soft-max attention over grouped heads: P[t] = [ q | k | v | head gates ] -> per-head norms, rotation, value mixing; keys and
+// values to the cache row of the token's position (and the means of the blocks this step completes to the pool) -> attention
+// under the layer's mask -> gate -> output product
+void mixer_gqattn(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) {
+    const int E = c->m->E, H = L.H, G = L.KH, D = L.D, V = L.V, nq = H * D, row = (int) L.cache_row, ldp = L.proj.N;
+    float * cache = c->caches[(size_t) R.cache_index], * pool = c->pools[(size_t) R.cache_index];
+    const StepState * st = &c->d_step->st;
+    linear(c, c->in, E, L.proj, c->P, ldp, T);
+    const GqaPrepArgs pa{c->P, ldp, H, G, D, V, L.qw, L.kw, c->m->eps, RopeArgs{L.rope_freq, L.rope_dims, 1.0f, L.rope_adjacent ? 1 : 0}, st, c->CV, cache, row,
+                         c->VF, L.vmode, L.vlambda};
+    k_gqa_prep<<<T, 256, 0, c->st>>>(pa);
+    c->launches++;
+    if (L.pool > 0) { k_pool_rows<<<T / L.pool + 1, 128, 0, c->st>>>(cache, row, pool, L.pool, st); c->launches++; }
+    const float * gate = L.head_gate ? c->P + nq + row : nullptr;
+    const GqaMask mask{L.mask_kind, L.window, L.pool};
+    const GqaScore sc{L.scale, L.cap};
+    if (T >= 8 && gqa_tiles_enabled()) {
+        // prompt portion: float32 products over tiles of ATT_TQ tokens, one batch entry per (tile, key/value head). A row's columns
+        // are [ block means | tokens ]; the token columns of a masked layer start `span` - 1 positions before the tile
+        const int TQ = ATT_TQ, Rh = H / G, M = TQ * Rh, ntile = (T + TQ - 1) / TQ, Tpad = ntile * TQ;
+        const int pos0 = c->h_step->st.pos0;
+        k_group_q_layout<<<Tpad, 256, 0, c->st>>>(c->CV, nq, T, Tpad, H, G, D, c->QK);
+        const bool masked = L.mask_kind != MASK_CAUSAL;
+        const int span = masked ? std::min(L.window, pos0 + Tpad) : 0;
+        const size_t nk_max = (size_t) ((masked ? span + TQ - 1 : pos0 + Tpad) + 3) / 4 * 4;
+        const int npc_max = (gqa_blocks_seen(mask, pos0 + T - 1) + 3) / 4 * 4;
+        const int per_group = (int) std::max<size_t>(1, c->att_scores_floats / ((size_t) G * M * (nk_max + npc_max)));
+        for (int g0 = 0; g0 < ntile; g0 += per_group) {
+            const int ng = std::min(per_group, ntile - g0);
+            const int nk = masked ? (int) nk_max : (pos0 + (g0 + ng) * TQ + 3) / 4 * 4;           // unmasked: no key beyond this group's last token is seen
+            const int npc = (gqa_blocks_seen(mask, pos0 + std::min(T, (g0 + ng) * TQ) - 1) + 3) / 4 * 4, ld = npc + nk;
+            const long long jlo = masked ? (long long) pos0 + (long long) g0 * TQ - span + 1 : 0; // may be negative: zero margin in front of the cache
+            const float * keys = cache + jlo * row;
+            const long long sK = masked ? (long long) TQ * row : 0;
+            const long long grp = (long long) ng * M * ld;
+            gemm_f32(c, c->QK + (size_t) g0 * M * D, D, (long long) M * D, keys, 0, row, sK, c->att_scores + npc, ld, (long long) M * ld, M, nk, D, ng,
+                     G, (long long) Tpad * Rh * D, D, grp);
+            if (npc) gemm_f32(c, c->QK + (size_t) g0 * M * D, D, (long long) M * D, pool, 0, row, 0, c->att_scores, ld, (long long) M * ld, M, npc, D, ng,
+                              G, (long long) Tpad * Rh * D, D, grp);
+            const int rows = ng * M * G;
+            k_gqa_softmax_rows<<<(rows + 7) / 8, 256, 0, c->st>>>(c->att_scores, ng * M, G, Rh, TQ, npc, nk, span, mask, sc, L.r1, L.r2, L.sink, st, g0, T);
+            gemm_f32(c, c->att_scores + npc, ld, (long long) M * ld, keys + (size_t) G * D, 1, row, sK, c->OL + (size_t) g0 * M * V, V, (long long) M * V, M, V, nk, ng,
+                     G, grp, V, (long long) Tpad * Rh * V);
+            if (npc) gemm_f32(c, c->att_scores, ld, (long long) M * ld, pool + (size_t) G * D, 1, row, 0, c->OL + (size_t) g0 * M * V, V, (long long) M * V, M, V, npc, ng,
+                              G, grp, V, (long long) Tpad * Rh * V, 1);
+            c->launches++;
+        }
+        k_group_o_layout<<<T, 256, 0, c->st>>>(c->OL, Tpad, H, G, V, c->A);
+        c->launches += 2;
+        if (gate) { k_head_gate<<<T, 256, 0, c->st>>>(c->A, gate, ldp, H, V, 0); c->launches++; }
+        linear(c, c->A, H * V, L.o, c->out, E, T);
+        return;
+    }
+    const int TQ = T >= 4 ? 4 : T >= 2 ? 2 : 1, WPQ = 8 / TQ;
+    const int blocks = ((T + TQ - 1) / TQ) * H;
+    const int max_keys = L.mask_kind == MASK_CAUSAL ? c->n_ctx : std::min(c->n_ctx, L.window + (L.pool > 0 ? c->n_ctx / L.pool : 0));
+    const int nsplit = std::max(1, std::min({ 2 * c->sm_count / blocks, ((max_keys + 31) / 32 + WPQ - 1) / WPQ, GQA_MAX_SPLIT }));
+    const GqaAttnArgs a{c->CV, nq, cache, pool, row, st, c->A, L.r1, L.r2, L.sink, gate, ldp, T, H, G, D, V, sc, mask, TQ,
+                        (D % 4 == 0 && row % 4 == 0 && ((uintptr_t) cache & 15) == 0 && ((uintptr_t) pool & 15) == 0) ? 1 : 0, nsplit, c->da_part, c->da_counter};
+    const dim3 grid((unsigned) ((T + TQ - 1) / TQ), (unsigned) H, (unsigned) nsplit);
+    const int VPL = gqa_vpl(L);
+    const size_t smem = ((size_t) TQ * D + (size_t) 8 * (2 + 32 * VPL)) * 4;
+    if (VPL == 1) k_gqa_attn<1><<<grid, 256, smem, c->st>>>(a);
+    else if (VPL == 2) k_gqa_attn<2><<<grid, 256, smem, c->st>>>(a);
+    else if (VPL == 4) k_gqa_attn<4><<<grid, 256, smem, c->st>>>(a);
+    else k_gqa_attn<8><<<grid, 256, smem, c->st>>>(a);
+    c->launches++;
+    linear(c, c->A, H * V, L.o, c->out, E, T);
+}
+
 void tap_layer(StackCtx * c, size_t ri, int T) {
     const size_t E = (size_t) c->m->E, n = (size_t) T * E;
     SCU(cudaMemcpyAsync(c->tap_data.data() + ri * n, c->X, n * 4, cudaMemcpyDeviceToHost, c->st));
@@ -1241,6 +1472,7 @@ void run_mixer(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) {
         case MIX_RETENTION: mixer_retention(c, L, R, T); break;
         case MIX_SIGATTN:   mixer_sigattn(c, L, R, T); break;
         case MIX_PAIR:      mixer_pair(c, L, R, T); break;
+        case MIX_GQATTN:    mixer_gqattn(c, L, R, T); break;
         case MIX_MINGRU:   mixer_mingru(c, L, R, T); break;
         case MIX_LATENT:   mixer_latent(c, L, R, T); break;
         case MIX_DELTA:    mixer_delta(c, L, R, T); break;
@@ -1335,11 +1567,11 @@ void enqueue_layers_parallel(StackCtx * c, int T) {
     SCU(cudaGetLastError());
 }
 
-// routed mixture on c->Hn: the chosen experts' outputs by slot in c->Yk (slot order in *slot_of: nullptr = t top + k), the
+// routed mixture on c->Hn (a design whose experts run on the weighted input gets outputs that are added as they are): the chosen experts' outputs by slot in c->Yk (slot order in *slot_of: nullptr = t top + k), the
 // shared unit's in c->Y; the layer's join weighs and adds them
 void mixture_ff(StackCtx * c, const LayerSpec & L, int T, const int32_t ** slot_of) {
     const int E = c->m->E, top = L.top, ff = L.e_ff, slots = T * top;
-    const RouteArgs ra{c->Hn, E, E, L.router, L.w_sg, L.n_exp, top, L.n_groups, L.keep_groups, L.r_scale, c->r_sel, c->r_wt, c->r_sg, c->r_z, c->r_counter};
+    const RouteArgs ra{c->Hn, E, E, L.router, L.w_sg, L.n_exp, top, L.n_groups, L.keep_groups, L.r_scale, c->r_sel, c->r_wt, c->r_sg, c->r_z, c->r_counter, L.route_fn};
     k_moe_route<<<dim3((unsigned) T, (unsigned) ((L.n_exp + (L.w_sg ? 1 : 0) + 7) / 8)), 256, (size_t) (2 * L.n_exp + L.n_groups) * 4, c->st>>>(ra);
     c->launches++;
     LinOpt o;
@@ -1347,8 +1579,9 @@ void mixture_ff(StackCtx * c, const LayerSpec & L, int T, const int32_t ** slot_
     if (T <= GEMV_MAX_T) {
         // few tokens: one mat-vec per (token, choice) against the chosen expert's matrices
         o.w_index = c->r_sel; o.x_share = top;
+        if (L.scale_input) o.x_scale = c->r_wt;     // W (w h) = w (W h): the weight meets the products before the gated unit
         linear(c, c->Hn, E, L.e_gateup, c->Ap, ff, 1, slots, E, ff, true, INFINITY, &o);
-        o.x_share = 1;
+        o.x_share = 1; o.x_scale = nullptr;
         linear(c, c->Ap, ff, L.e_down, c->Yk, E, 1, slots, ff, E, false, 0.f, &o);
         *slot_of = nullptr;
     } else {
@@ -1358,7 +1591,8 @@ void mixture_ff(StackCtx * c, const LayerSpec & L, int T, const int32_t ** slot_
         const size_t cnt_bytes = (size_t) L.n_exp * tpe * 4;
         const int in_smem = (size_t) slots * 4 + cnt_bytes <= 40 * 1024 ? 1 : 0;
         k_moe_sort<<<1, 1024, cnt_bytes + (in_smem ? (size_t) slots * 4 : 0), c->st>>>(c->r_sel, slots, top, L.n_exp, tpe, in_smem, c->r_seg, c->r_slot, c->r_src);
-        k_gather_rows<<<slots, 128, 0, c->st>>>(c->Hn, E, c->r_src, E, c->Xp);
+        if (L.scale_input) k_spread_rows<<<slots, 128, 0, c->st>>>(c->Hn, E, c->r_slot, c->r_wt, top, E, c->Xp);
+        else k_gather_rows<<<slots, 128, 0, c->st>>>(c->Hn, E, c->r_src, E, c->Xp);
         c->launches += 2;
         o.seg = c->r_seg;
         linear(c, c->Xp, E, L.e_gateup, c->Ap, ff, slots, L.n_exp, 0, 0, true, INFINITY, &o);
@@ -1418,10 +1652,55 @@ void enqueue_layers_prenorm(StackCtx * c, int T) {
     SCU(cudaGetLastError());
 }
 
+// hyper-connected blocks: the residual is m.streams rows per token; every sub-layer ends in one k_hc_join launch that writes all
+// streams and norms the read-in of the sub-layer that follows. c->X gets the sum of the streams where it is wanted (taps, the head).
+void enqueue_layers_hyper(StackCtx * c, int T) {
+    StackModel & m = *c->m;
+    const int E = m.E, S = m.streams;
+    const long long plane = (long long) c->cap * E;
+    {
+        const LayerSpec & L0 = m.layers[(size_t) m.runs[0].layer];
+        if (m.dtype == STACK_F32) k_hc_embed<float><<<T, 256, 0, c->st>>>((const float *) m.embed, c->d_step->tokens, E, m.vocab, S, c->XS, plane, L0.hc[0], L0.g1, m.eps, c->Hn);
+        else k_hc_embed<__nv_bfloat16><<<T, 256, 0, c->st>>>((const __nv_bfloat16 *) m.embed, c->d_step->tokens, E, m.vocab, S, c->XS, plane, L0.hc[0], L0.g1, m.eps, c->Hn);
+        c->launches++;
+    }
+    for (size_t ri = 0; ri < m.runs.size(); ri++) {
+        const RunSpec & R = m.runs[ri];
+        const LayerSpec & L = m.layers[(size_t) R.layer];
+        const LayerSpec * N = ri + 1 < m.runs.size() ? &m.layers[(size_t) m.runs[ri + 1].layer] : nullptr;      // the final norm runs on the wanted rows only
+        const bool want_sum = c->taps || !N;
+        const auto join = [&](int q, HcJoinArgs & j) {
+            j.XS = c->XS; j.plane = plane; j.S = S; j.E = E; j.eps = m.eps;
+            j.w = L.hc[q];
+            const bool last_sub = q == 1 || !L.has_mlp;
+            const HcW * nw = !last_sub ? &L.hc[1] : N ? &N->hc[0] : nullptr;
+            if (nw) { for (int s = 0; s < HC_MAX; s++) j.nin[s] = nw->in[s]; j.g = !last_sub ? L.g2 : N->g1; j.Hn = c->Hn; }
+            if (last_sub && want_sum) j.Xsum = c->X;
+            k_hc_join<<<T, 256, 0, c->st>>>(j);
+            c->launches++;
+        };
+        c->in = c->Hn; c->out = c->Y;
+        run_mixer(c, L, R, T);
+        HcJoinArgs j{};
+        j.Ya = c->Y;
+        join(0, j);
+        if (L.has_mlp) {
+            HcJoinArgs f{};
+            mixture_ff(c, L, T, &f.slot_of);
+            f.Yk = c->Yk; f.top = L.top;
+            if (L.ff > 0) f.Ya = c->Y;
+            join(1, f);
+        }
+        if (c->taps) tap_layer(c, ri, T);
+    }
+    SCU(cudaGetLastError());
+}
+
 // the layers over the T tokens whose header (positions, ids) is already on the device
 void enqueue_layers(StackCtx * c, int T) {
     if (c->m->block == BLOCK_PARALLEL) enqueue_layers_parallel(c, T);
     else if (c->m->block == BLOCK_PRENORM) enqueue_layers_prenorm(c, T);
+    else if (c->m->block == BLOCK_HYPER) enqueue_layers_hyper(c, T);
     else enqueue_layers_sequential(c, T);
 }
 
@@ -1523,6 +1802,8 @@ void stack_ctx_free(StackCtx * c) {
     if (c->g_token) cudaGraphExecDestroy(c->g_token);
     if (c->g_greedy) cudaGraphExecDestroy(c->g_greedy);
     cudaFree(c->d_out_tokens); cudaFree(c->d_counter);
+    for (float * p : c->pools) cudaFree(p);
+    for (float * p : { c->XS, c->VF }) cudaFree(p);
     for (float * p : { c->Y2, c->U, c->XC, c->keep, c->ret_sb, c->Xp, c->Ap, c->Yk, c->r_wt, c->r_sg, c->r_z }) cudaFree(p);
     cudaFree(c->r_counter);
     for (int32_t * p : { c->r_sel, c->r_slot, c->r_src, c->r_seg }) cudaFree(p);
@@ -1553,6 +1834,8 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
         if (par) { fl(&c->Y2, cap * m->E); fl(&c->U, cap * m->E * 2); fl(&c->XC, cap * m->E * 2); }
         else if (m->has_pair) fl(&c->Y2, cap * m->E);
         if (m->depth_avg) fl(&c->keep, (m->layers.size() + 1) * cap * m->E);
+        if (m->block == BLOCK_HYPER) fl(&c->XS, (size_t) m->streams * cap * m->E);
+        if (m->vfirst_width > 0) fl(&c->VF, cap * (size_t) m->vfirst_width);
         if (m->max_ret_state > 0 && c->cap >= RET_CHUNK_MIN_T) {
             fl(&c->ret_sb, (size_t) ((c->cap + RC - 1) / RC) * m->max_ret_state);
             static size_t attr = 48 * 1024;
@@ -1576,6 +1859,7 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
         SCU(cudaMalloc(&c->d_err, 4)); SCU(cudaMemsetAsync(c->d_err, 0, 4, c->st));
         SCU(cudaMallocHost(&c->h_err, 4)); *c->h_err = 0;
         c->caches.assign((size_t) m->n_caches, nullptr);
+        c->pools.assign((size_t) m->n_caches, nullptr);
         cudaDeviceProp prop;
         SCU(cudaGetDeviceProperties(&prop, m->device));
         c->sm_count = prop.multiProcessorCount;
@@ -1597,7 +1881,12 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
                 fl(&base, rows * L.cache_row);
                 c->cache_allocs.push_back(base);
                 c->caches[(size_t) cd.index] = base + front * L.cache_row;
-                const size_t nk = (L.window > 0 ? (size_t) L.window + ATT_TQ - 1 : (size_t) n_ctx + ATT_TQ) + 3;
+                size_t nk = (L.window > 0 ? (size_t) L.window + ATT_TQ - 1 : (size_t) n_ctx + ATT_TQ) + 3;
+                if (L.pool > 0) {             // means of whole blocks: [ n_ctx / pool rows | a tile of slack for padded products ]
+                    const size_t prow = (size_t) n_ctx / (size_t) L.pool + ATT_TQ;
+                    fl(&c->pools[(size_t) cd.index], prow * L.cache_row);
+                    nk += prow;
+                }
                 const size_t one = (size_t) ATT_TQ * L.H * nk * (L.kind == MIX_DIFFATTN ? 2 : 1);     // one tile's scores (two maps per head)
                 const size_t all = (cap_t / ATT_TQ) * one;
                 c->att_scores_floats = std::max(c->att_scores_floats, std::min(all, std::max(one, ATT_SCORE_BYTES / 4)));
@@ -1611,6 +1900,11 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
             if (L.kind == MIX_SIGATTN) {
                 da_part = std::max(da_part, (size_t) 8 * L.H * SIG_MAX_SPLIT * 32 * (size_t) sig_vpl(L));
                 da_cnt = std::max(da_cnt, (size_t) 8 * L.H);
+                continue;
+            }
+            if (L.kind == MIX_GQATTN) {       // key slices only while (tokens x heads x slices) stays under 8 per SM; one counter per (token, head) of a pass
+                da_part = std::max(da_part, (size_t) (8 * c->sm_count + 64) * (2 + 32 * (size_t) gqa_vpl(L)));
+                da_cnt = std::max(da_cnt, cap * (size_t) L.H);
                 continue;
             }
             for (int T = 1; T <= std::min(c->cap, 7); T++) {      // the pass sizes that take the decode kernels: the buffers cover the largest plan

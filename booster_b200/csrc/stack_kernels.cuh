@@ -158,6 +158,9 @@ struct LinArgs {
     // k_gemv: entry z meets matrix w_index[z] of the batch and reads the rows of entry z / x_share
     const int32_t * w_index = nullptr;
     int x_share = 1;
+    // k_gemv: entry z's input row is x_scale[z] times the row it reads (a routed expert that runs on a weighted input); no bias then
+    const float * x_scale = nullptr;
+    int accum = 0;      // k_gemm_simt only: Y += the product (a second set of keys joining a weighted sum)
 };
 __device__ __forceinline__ float clamped_glu(float gate, float up, float limit, float alpha, float shift) {
     const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);      // limit = +inf: no clamp
@@ -238,7 +241,7 @@ __global__ void __launch_bounds__(256) k_gemv(const LinArgs a) {
         if (t < a.T) {
             float s[RPW];
 #pragma unroll
-            for (int r = 0; r < RPW; r++) s[r] = warp_sum(acc[r][t]) + (a.bias ? a.bias[n + r] : 0.f);
+            for (int r = 0; r < RPW; r++) s[r] = warp_sum(acc[r][t]) * (a.x_scale ? a.x_scale[blockIdx.z] : 1.0f) + (a.bias ? a.bias[n + r] : 0.f);
             if (lane == 0) {
                 float * y = a.Y + (size_t) blockIdx.z * a.sY + (size_t) t * a.ldy;
                 if constexpr (RPW == 2) y[n >> 1] = clamped_glu(s[0], s[1], a.limit, a.alpha, a.up_shift);
@@ -325,7 +328,7 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const LinArgs a) {
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int n = n0 + tx * 4 + j;
-            if (n < a.N) Y[(size_t) m * a.ldy + n] = acc[i][j] + (a.bias ? a.bias[n] : 0.f);
+            if (n < a.N) Y[(size_t) m * a.ldy + n] = acc[i][j] + (a.bias ? a.bias[n] : 0.f) + (a.accum ? Y[(size_t) m * a.ldy + n] : 0.f);
         }
     }
 }
@@ -619,12 +622,16 @@ __global__ void k_mingru_scan(const float * __restrict__ P, int T, int width, fl
     state[c] = s;
 }
 
-// ---- rotary positions, 'rotate half' pairing (i, i + dims/2) on the first `dims` entries of a vector -------------------------
+// ---- rotary positions on the first `dims` entries of a vector: pair i is (i, i + dims/2) ('rotate half') or, with
+// adjacent = 1, the neighbours (2i, 2i + 1) -------------------------------------------------------------------------------
 struct RopeArgs {
     const float * freq;   // [dims / 2] frequencies after any YaRN blend (host-built)
     int dims;
     float mag;            // factor on cos and sin (YaRN: 0.1 ln(factor) + 1; else 1)
+    int adjacent;         // 0: pair i = entries (i, i + dims/2); 1: entries (2i, 2i + 1)
 };
+__device__ __forceinline__ int rope_lo(const RopeArgs & r, int i) { return r.adjacent ? 2 * i : i; }
+__device__ __forceinline__ int rope_hi(const RopeArgs & r, int i) { return r.adjacent ? 2 * i + 1 : i + r.dims / 2; }
 __device__ __forceinline__ void rope_pair(const RopeArgs & r, int pos, int i, float u, float v, float & ou, float & ov) {
     const float ang = (float) pos * r.freq[i];
     const float c = cosf(ang) * r.mag, s = sinf(ang) * r.mag;
@@ -662,8 +669,8 @@ __global__ void k_latent_prep(float * __restrict__ P, int ldp, int H, int D, int
         const float * src = v == H ? dkv + rank : p + (size_t) v * (D + R) + D;
         float * dst = v == H ? row + rank : QK + ((size_t) t * H + v) * (rank + R) + rank;
         for (int i = lane; i < R; i += 32) {
-            if (i < half) { float a, b; rope_pair(rope, pos, i, src[i], src[i + half], a, b); dst[i] = a; dst[i + half] = b; }
-            else if (i >= rope.dims) dst[i] = src[i];
+            if (i < half) { const int lo = rope_lo(rope, i), hi = rope_hi(rope, i); float a, b; rope_pair(rope, pos, i, src[lo], src[hi], a, b); dst[lo] = a; dst[hi] = b; }
+            if (i >= rope.dims) dst[i] = src[i];
         }
     }
 }
@@ -1560,10 +1567,11 @@ __global__ void __launch_bounds__(256) k_polynorm(float * __restrict__ Z, int n,
 }
 
 // ---- small element-wise steps ---------------------------------------------------------------------------------------------------
-// per-head output gate: A[t][h][0..V) *= sigmoid(gate[t][h]) (gate rows of stride ldg)
-__global__ void k_head_gate(float * __restrict__ A, const float * __restrict__ gate, int ldg, int H, int V) {
+// output gate: A[t][h][0..V) *= sigmoid(gate[t][h]) (one number per head), or with per_entry = 1 A[t][i] *= sigmoid(gate[t][i])
+// (one number per entry); gate rows of stride ldg
+__global__ void k_head_gate(float * __restrict__ A, const float * __restrict__ gate, int ldg, int H, int V, int per_entry) {
     const int t = blockIdx.x;
-    for (int i = threadIdx.x; i < H * V; i += blockDim.x) A[(size_t) t * H * V + i] *= sigmoidf_(gate[(size_t) t * ldg + i / V]);
+    for (int i = threadIdx.x; i < H * V; i += blockDim.x) A[(size_t) t * H * V + i] *= sigmoidf_(gate[(size_t) t * ldg + (per_entry ? i : i / V)]);
 }
 // soft cap on the logits: x <- cap tanh(x / cap)
 __global__ void k_softcap(float * __restrict__ x, size_t n, float cap) {

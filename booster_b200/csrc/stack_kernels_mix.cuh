@@ -615,7 +615,8 @@ __global__ void k_group_o_layout(const float * __restrict__ Or, int Tpad, int H,
 }
 
 // ---- routed mixture of gated units --------------------------------------------------------------------------------------------------
-// Router, per token, in float32: z = W_r h, s = softmax(z) over all n experts. The expert list is cut into n_groups consecutive blocks
+// Router, per token, in float32: z = W_r h, s = softmax(z) over all n experts (score_fn 0) or s_i = sigmoid(z_i), each expert by
+// itself (score_fn 1). The expert list is cut into n_groups consecutive blocks
 // of equal size; a block ranks by the best s inside it and the choice is confined to the `keep` best-ranked blocks: of their experts
 // the `top` with the largest s are taken (lowest index first among equals), each weighing in with s * scale as it is.
 // sel[t][top], wt[t][top]; sg[t] = sigmoid(w_sg . h) is the shared unit's gate (w_sg == nullptr: no shared unit).
@@ -629,6 +630,7 @@ struct RouteArgs {
     float scale;
     int32_t * sel; float * wt; float * sg;
     float * z; int * counter;
+    int score_fn;       // 0: soft-max over the experts; 1: sigmoid of each logit
 };
 __global__ void __launch_bounds__(256) k_moe_route(const RouteArgs a) {
     extern __shared__ float rsm[];
@@ -663,15 +665,19 @@ __global__ void __launch_bounds__(256) k_moe_route(const RouteArgs a) {
         if (threadIdx.x == 0) a.counter[t] = 0;
     } else __syncthreads();
     if (warp != 0) return;
-    float mx = -INFINITY;
-    for (int i = lane; i < a.n; i += 32) { const float v = __ldcg(z + i); s[i] = v; mx = fmaxf(mx, v); }
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int i = lane; i < a.n; i += 32) { const float v = expf(s[i] - mx); s[i] = v; sum += v; }
-    sum = warp_sum(sum);
-    const float inv = 1.0f / sum;
     const int per = a.n / a.n_groups;
-    for (int i = lane; i < a.n; i += 32) { s[i] *= inv; elig[i] = -1.f; }
+    if (a.score_fn == 1) {
+        for (int i = lane; i < a.n; i += 32) { s[i] = sigmoidf_(__ldcg(z + i)); elig[i] = -1.f; }
+    } else {
+        float mx = -INFINITY;
+        for (int i = lane; i < a.n; i += 32) { const float v = __ldcg(z + i); s[i] = v; mx = fmaxf(mx, v); }
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int i = lane; i < a.n; i += 32) { const float v = expf(s[i] - mx); s[i] = v; sum += v; }
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sum;
+        for (int i = lane; i < a.n; i += 32) { s[i] *= inv; elig[i] = -1.f; }
+    }
     __syncwarp();
     for (int g = lane; g < a.n_groups; g += 32) {
         float b = -1.f;
@@ -763,6 +769,16 @@ __global__ void k_gather_rows(const float * __restrict__ X, int ldx, const int32
     } else {
         for (int i = threadIdx.x; i < E; i += blockDim.x) Y[(size_t) r * E + i] = x[i];
     }
+}
+
+// Y[slot_of[s]] = wt[s] X[s / top]: every (token, choice) slot's input row, weighted by the choice's score, at the row the sort
+// gave the slot (an expert that runs on the weighted input)
+__global__ void k_spread_rows(const float * __restrict__ X, int ldx, const int32_t * __restrict__ slot_of, const float * __restrict__ wt, int top, int E, float * __restrict__ Y) {
+    const int s = blockIdx.x;
+    const float * x = X + (size_t) (s / top) * ldx;
+    float * y = Y + (size_t) slot_of[s] * E;
+    const float w = wt[s];
+    for (int i = threadIdx.x; i < E; i += blockDim.x) y[i] = w * x[i];
 }
 
 }  // namespace stk
