@@ -302,6 +302,28 @@ def bench_tosevik(args):
     return 0
 
 
+def bench_rumurax(args):
+    """`--family stack --stack-design rumurax`: prefill and decode throughput of the Rumurax design (bfloat16 weights; random) at
+    sizes resembling real layers, beside the closest existing model, the Tosevik design (pre-norm sub-layers, an attention over
+    grouped heads with a float32 cache, a routed mixture with a shared unit), at equal width / layers / heads / vocabulary and
+    with as many feed-forward units read per token. Comparable figures: the decode fraction of the measured HBM bandwidth and the
+    prefill rate in weight bytes x tokens per second."""
+    from booster_b200 import _lib, engine, stack_io
+    L = _lib.lib()
+    hbm, hbm_src = peaks()
+    out = {"family": "stack", "design": "Rumurax", "closest": "Tosevik", "dtype": "bf16", "data": "synthetic (random bfloat16 weights)", "hbm_gbs_peak": hbm,
+           "hbm_peak_source": hbm_src, "steps": args.steps, "warmup": args.warmup, "sizes": {}}
+    for name, sz in STACK_SIZES.items():
+        if args.stack_size and name != args.stack_size:
+            continue
+        res = {}
+        res["rumurax"] = time_stack_model(engine, L, stack_io, stack_io.rumurax_config(**sz), os.path.join(MODEL_DIR, f"rumurax_{name}_s1234"), args, hbm)
+        res["tosevik"] = time_stack_model(engine, L, stack_io, stack_io.tosevik_config(**sz), os.path.join(MODEL_DIR, f"tosevik_{name}_s1234"), args, hbm)
+        out["sizes"][name] = res
+    print(json.dumps(out))
+    return 0
+
+
 def bench_stack(args):
     """Prefill and decode throughput of the Matulorn design (bfloat16 weights; random) at sizes resembling real layers, the
     LLaMA path (Q8_0, the closest block format in bytes per weight) at equal width / ff / layers / vocabulary beside it, and
@@ -407,11 +429,11 @@ def main():
     ap.add_argument("--family", default="llama", choices=["llama", "stack"],
                     help="stack: the layer-stack family (Matulorn design) beside the LLaMA path at equal layer sizes; the default workload is untouched")
     ap.add_argument("--stack-size", default="", choices=[""] + sorted(STACK_SIZES), help="--family stack: one size only")
-    ap.add_argument("--stack-design", default="matulorn", choices=["matulorn", "dopilorn", "tosevik"],
-                    help="--family stack: which design is measured (matulorn beside the LLaMA path; dopilorn beside matulorn; tosevik beside dopilorn)")
+    ap.add_argument("--stack-design", default="matulorn", choices=["matulorn", "dopilorn", "tosevik", "rumurax"],
+                    help="--family stack: which design is measured (matulorn beside the LLaMA path; dopilorn beside matulorn; tosevik beside dopilorn; rumurax beside tosevik)")
     args = ap.parse_args()
     if args.family == "stack":
-        return bench_tosevik(args) if args.stack_design == "tosevik" else bench_dopilorn(args) if args.stack_design == "dopilorn" else bench_stack(args)
+        return bench_rumurax(args) if args.stack_design == "rumurax" else bench_tosevik(args) if args.stack_design == "tosevik" else bench_dopilorn(args) if args.stack_design == "dopilorn" else bench_stack(args)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

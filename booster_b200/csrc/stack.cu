@@ -156,7 +156,7 @@ struct StackModel {
     bool has_pair = false;
     int streams = 1;                      // BLOCK_HYPER: copies of the residual
     bool rope_adjacent = false;           // the design rotates neighbouring pairs
-    int vfirst_width = 0;                 // key/value heads x vdim of the first value-mixing layer (0: none so far)
+    int vfirst_width = 0, vfirst_heads = 0;   // key/value heads x vdim, and key/value heads, of the first value-mixing layer (0: none so far)
     int max_slots = 0, max_eff = 0, max_exp = 0;      // routed mixtures: choices per token, expert width, experts
     size_t max_ret_state = 0;             // retention: the largest heads x dim x vdim
     int max_ret_dim = 0;
@@ -555,9 +555,9 @@ void load_gqattn(StackModel & m, LayerSpec & L, const Json & mx, const safetenso
     if (sf.find(p + "sink")) L.sink = up_f32(m, sf.read_f32(p + "sink", {H}));
     L.vmode = GQA_V_PLAIN;
     if (mx.has("v_mix") && mx.at("v_mix").kind == Json::Bool && mx.at("v_mix").b) {
-        if (m.vfirst_width == 0) { L.vmode = GQA_V_FIRST; m.vfirst_width = G * V; }      // the first mixing layer's own weight is unused
+        if (m.vfirst_width == 0) { L.vmode = GQA_V_FIRST; m.vfirst_width = G * V; m.vfirst_heads = G; }      // the first mixing layer's own weight is unused
         else {
-            if (m.vfirst_width != G * V) throw std::runtime_error("config: value-mixing layers must agree in kv_heads x vdim");
+            if (m.vfirst_width != G * V || m.vfirst_heads != G) throw std::runtime_error("config: value-mixing layers must agree in kv_heads and vdim");
             L.vmode = GQA_V_MIX;
             L.vlambda = read_scalar(sf, p + "vmix");
         }

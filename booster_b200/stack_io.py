@@ -1,4 +1,4 @@
-"""Synthetic models of the layer-stack family (Matulorn, Dopilorn and Tosevik designs; config.json + model.safetensors) for benchmarks and smoke runs: random
+"""Synthetic models of the layer-stack family (Matulorn, Dopilorn, Tosevik and Rumurax designs; config.json + model.safetensors) for benchmarks and smoke runs: random
 bfloat16 weights of the right shapes, the counterpart of gguf_io.synth_llama for the GGUF path. Pure host code."""
 from __future__ import annotations
 
@@ -75,6 +75,63 @@ def tosevik_config(width: int, n_layer: int, ff: int, heads: int, vocab: int = 3
                "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": groups[0], "keep": groups[1]}}}
         layers.append({"type": kind, "mixer": mx, "mlp": mlp})
     return {"architecture": "Tosevik", "layers": layers, "norm": {"eps": 1e-6}, "vocab": vocab, "width": width}
+
+
+def rumurax_config(width: int, n_layer: int, ff: int, heads: int, vocab: int = 32000, head_dim: int = 128, kv_heads: int = 0, experts: int = 16, top: int = 4,
+                   streams: int = 4, window: int = 1024, pool: int = 32, chunk: int = 1024, kv_rank: int = 512, rot_dim: int = 64,
+                   pattern=("attention_2", "attention", "latent_attention", "attention")) -> dict:
+    """a Rumurax configuration whose layers resemble a real model's: mixers in `pattern` order, a routed mixture on every layer whose
+    chosen experts plus the shared unit are as wide together as a dense feed-forward of `ff` (top x 3 ff / 16 + ff / 4)"""
+    e_ff = max(8, ff * 3 // (4 * top) // 8 * 8)
+    G = kv_heads or max(1, heads // 4)
+    layers = []
+    for i in range(n_layer):
+        kind = pattern[i % len(pattern)]
+        if kind == "attention_2":
+            mx = {"heads": heads, "kv_heads": G, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "mask": {"size": window, "pool": pool},
+                  "rot": {"base": 500000.0, "dims": head_dim // 2}, "v_mix": True}
+        elif kind == "attention":
+            mx = {"heads": heads, "kv_heads": G, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "mask": {"size": chunk}, "softcap": 50.0, "v_mix": True}
+        else:
+            mx = {"heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "kv_rank": kv_rank, "scale": (head_dim + rot_dim) ** -0.5,
+                  "rot": {"base": 500000.0, "dims": rot_dim}}
+        mlp = {"kind": "moe", "expert": {"ff": e_ff}, "shared": {"ff": ff - top * e_ff}, "router": {"experts": experts, "top": top}}
+        layers.append({"type": kind, "mixer": mx, "mlp": mlp})
+    return {"architecture": "Rumurax", "layers": layers, "norm": {"eps": 1e-6}, "streams": streams, "vocab": vocab, "width": width}
+
+
+def rumurax_shapes(cfg: dict) -> Dict[str, List[int]]:
+    E, V, S = cfg["width"], cfg["vocab"], cfg.get("streams", 1)
+    t: Dict[str, List[int]] = {"embed": [V, E]}
+    for i, L in enumerate(cfg["layers"]):
+        p, mx = f"l{i}.", L["mixer"]
+        for q in ((1, 2) if L.get("mlp") else (1,)):
+            t.update({f"{p}norm{q}": [], f"{p}hc{q}.in": [S], f"{p}hc{q}.out": [S], f"{p}hc{q}.mix": [S, S]})
+        H, D, Vd, m = mx["heads"], mx["dim"], mx["vdim"], p + "mix."
+        if L["type"] == "latent_attention":
+            R, rank = mx.get("rot_dim", 0), mx["kv_rank"]
+            t.update({m + "q": [H * (D + R), E], m + "dkv": [rank + R, E], m + "dkv.norm": [rank], m + "uk": [H * D, rank], m + "uv": [H * Vd, rank],
+                      m + "g": [H * Vd, E], m + "o": [E, H * Vd]})
+        elif L["type"] in ("attention", "attention_2"):
+            G = mx.get("kv_heads", H)
+            t.update({m + "q": [H * D, E], m + "k": [G * D, E], m + "v": [G * Vd, E], m + "q.norm": [D], m + "k.norm": [D], m + "o": [E, H * Vd]})
+            if mx.get("v_mix"):
+                t[m + "vmix"] = []
+            if L["type"] == "attention":
+                t.update({m + "r1": [H], m + "r2": [H], m + "sink": [H], m + "g": [H, E]})
+        else:
+            raise ValueError(L["type"])
+        mj = L.get("mlp")
+        if mj:
+            units = [(f"e{e}.", mj["expert"]["ff"]) for e in range(mj["router"]["experts"])]
+            if mj.get("shared"):
+                units.append(("shared.", mj["shared"]["ff"]))
+            for u, f in units:
+                t.update({p + "mlp." + u + "gate": [f, E], p + "mlp." + u + "up": [f, E], p + "mlp." + u + "down": [E, f]})
+            t[p + "mlp.router"] = [mj["router"]["experts"], E]
+    t["final.norm"] = []
+    t["head"] = [V, E]
+    return t
 
 
 def tosevik_shapes(cfg: dict) -> Dict[str, List[int]]:
@@ -168,6 +225,8 @@ def tensor_shapes(cfg: dict) -> Dict[str, List[int]]:
         return dopilorn_shapes(cfg)
     if cfg.get("architecture") == "Tosevik":
         return tosevik_shapes(cfg)
+    if cfg.get("architecture") == "Rumurax":
+        return rumurax_shapes(cfg)
     E, V = cfg["width"], cfg["vocab"]
     t = {"embed": [V, E]}
     for i, L in enumerate(cfg["layers"]):
@@ -224,6 +283,17 @@ def synth_stack(d: str, cfg: dict, seed: int = 1234) -> str:
                     x = np.full(1, 0.75, np.float32)
                 else:
                     x = 0.1 * rng.standard_normal(n, dtype=np.float32) - (1.0 if leaf == "pb" else 0.0)
+            elif cfg.get("architecture") == "Rumurax" and (".hc" in name or leaf in ("r1", "r2", "vmix")):
+                if leaf == "mix":                                # keep every stream, leak a little into the others
+                    x = (np.eye(shp[0], dtype=np.float32) + 0.05 * rng.standard_normal(shp, dtype=np.float32)).reshape(-1)
+                elif leaf == "in":                               # read the streams' mean
+                    x = np.full(n, 1.0 / n, np.float32) + 0.02 * rng.standard_normal(n, dtype=np.float32)
+                elif leaf == "out":
+                    x = 0.5 + 0.1 * rng.standard_normal(n, dtype=np.float32)
+                elif leaf == "vmix":
+                    x = np.full(1, 0.5, np.float32)
+                else:                                            # positive: the penalty is r1 ln(1 + r2 distance)
+                    x = 0.1 + rng.random(n, dtype=np.float32)
             elif name.endswith("mlp.act"):
                 x = np.array([1.0, 0.5, 0.25, 0.0], np.float32)
             elif "canon" in name or zero_centred or name == "loop.step":

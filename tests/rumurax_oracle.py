@@ -18,6 +18,10 @@ name. Notation: T tokens, E width, S streams, H query heads, G key/value heads, 
 import numpy as np
 
 
+def scalar(x):
+    return float(np.asarray(x).reshape(-1)[0])
+
+
 def rms_unit(x, eps):
     return x / np.sqrt(np.mean(x * x, axis=-1, keepdims=True) + eps)
 
@@ -81,7 +85,7 @@ def attention(h, mx, W, pre, eps, kind, v_first):
         q = rotate_pairs(q, pos, mx["rot"]["base"], mx["rot"]["dims"])
         k = rotate_pairs(k, pos, mx["rot"]["base"], mx["rot"]["dims"])
     if mx.get("v_mix") and v_first is not None:
-        lam = float(W[pre + "vmix"])
+        lam = scalar(W[pre + "vmix"])
         v = (1.0 - lam) * v + lam * v_first
     n = mx["mask"]["size"]
     P = mx["mask"].get("pool", 0) if kind == "window" else 0
@@ -182,7 +186,7 @@ def forward(cfg, W, tokens):
             else:
                 a, M, b = np.ones(1), np.ones((1, 1)), np.ones(1)
             u = np.tensordot(a, xs, axes=(0, 0))
-            hn = rms_unit(u, eps) * float(W[p + "norm%d" % q])
+            hn = rms_unit(u, eps) * scalar(W[p + "norm%d" % q])
             if q == 2:
                 y = mixture(hn, lj["mlp"], W, p + "mlp.")
             elif lj["type"] == "latent_attention":
@@ -195,5 +199,90 @@ def forward(cfg, W, tokens):
             xs = np.tensordot(M.T, xs, axes=(1, 0)) + b[:, None, None] * y[None]
         taps.append(xs.sum(axis=0))
     x = xs.sum(axis=0)
-    logits = (rms_unit(x, eps) * float(W["final.norm"])) @ W["head"].T
+    logits = (rms_unit(x, eps) * scalar(W["final.norm"])) @ W["head"].T
     return logits, np.stack(taps)
+
+
+def tensor_shapes(cfg):
+    """tensor name -> shape of a model file of this design"""
+    E, Vc, S = cfg["width"], cfg["vocab"], cfg.get("streams", 1)
+    t = {"embed": [Vc, E]}
+    for i, lj in enumerate(cfg["layers"]):
+        p, mx = "l%d." % i, lj["mixer"]
+        subs = (1, 2) if lj.get("mlp") else (1,)
+        for q in subs:
+            t[p + "norm%d" % q] = []
+            t[p + "hc%d.in" % q] = [S]
+            t[p + "hc%d.out" % q] = [S]
+            t[p + "hc%d.mix" % q] = [S, S]
+        m = p + "mix."
+        H, D, V = mx["heads"], mx["dim"], mx["vdim"]
+        if lj["type"] == "latent_attention":
+            R, rank = mx.get("rot_dim", 0), mx["kv_rank"]
+            t.update({m + "q": [H * (D + R), E], m + "dkv": [rank + R, E], m + "dkv.norm": [rank], m + "uk": [H * D, rank], m + "uv": [H * V, rank],
+                      m + "g": [H * V, E], m + "o": [E, H * V]})
+        else:
+            G = mx.get("kv_heads", H)
+            t.update({m + "q": [H * D, E], m + "k": [G * D, E], m + "v": [G * V, E], m + "q.norm": [D], m + "k.norm": [D], m + "o": [E, H * V]})
+            if mx.get("v_mix"):
+                t[m + "vmix"] = []
+            if lj["type"] == "attention":
+                t.update({m + "r1": [H], m + "r2": [H], m + "sink": [H], m + "g": [H, E]})
+        if lj.get("mlp"):
+            mj, f = lj["mlp"], p + "mlp."
+            units = [("e%d." % e, mj["expert"]["ff"]) for e in range(mj["router"]["experts"])]
+            if mj.get("shared"):
+                units.append(("shared.", mj["shared"]["ff"]))
+            for u, ff in units:
+                t.update({f + u + "gate": [ff, E], f + u + "up": [ff, E], f + u + "down": [E, ff]})
+            t[f + "router"] = [mj["router"]["experts"], E]
+    t["final.norm"] = []
+    t["head"] = [Vc, E]
+    return t
+
+
+def random_model(cfg, seed=0):
+    """random weights rounded to bfloat16 (what a model file holds): matrices ~ N(0, 1/in), norm weights near 1, router rows spread
+    so that the choice of experts is never a close call, stream weights near (read the mean, keep every stream, write to all)"""
+    import stack_oracle as so
+    rng = np.random.default_rng(seed)
+    S = cfg.get("streams", 1)
+    W = {}
+    for name, shp in tensor_shapes(cfg).items():
+        leaf = name.rsplit(".", 1)[-1]
+        if ".hc" in name:
+            if leaf == "in":
+                x = 1.0 / S + 0.2 * rng.standard_normal(shp)
+            elif leaf == "out":
+                x = 1.0 + 0.3 * rng.standard_normal(shp)
+            else:
+                x = np.eye(S) + 0.2 * rng.standard_normal(shp)
+        elif leaf == "router":
+            x = rng.standard_normal(shp) * (3.0 / np.sqrt(shp[1]))
+        elif leaf == "r1":
+            x = 0.3 + 0.5 * rng.random(shp)
+        elif leaf == "r2":
+            x = 0.2 + 1.5 * rng.random(shp)
+        elif leaf == "sink":
+            x = rng.standard_normal(shp)
+        elif leaf == "vmix":
+            x = np.asarray(0.25 + 0.5 * rng.random())
+        elif len(shp) == 2:
+            x = rng.standard_normal(shp) / np.sqrt(shp[1])
+        elif len(shp) == 0:
+            x = np.asarray(1.0 + 0.1 * rng.standard_normal())
+        else:
+            x = 1.0 + 0.1 * rng.standard_normal(shp)
+        W[name] = so.round_bf16(np.asarray(x, np.float32)).astype(np.float64).reshape(shp)
+    return W
+
+
+def write_model(d, cfg, W):
+    import json
+    import os
+    import stack_oracle as so
+    os.makedirs(d, exist_ok=True)
+    so.save_safetensors(os.path.join(d, "model.safetensors"), {k: np.asarray(v, np.float32) for k, v in W.items()})
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    return d
