@@ -288,7 +288,7 @@ static DevMat upload_named(const gguf_file & g, const std::string & name, int64_
 
 extern "C" void b200_model_free(b200_model * m);
 // Model registry, by container: a folder with config.json + model.safetensors names its design in "architecture" and is
-// built by the layer-stack family (stack.cu: Matulorn, Dopilorn, Tosevik); a GGUF file names general.architecture (llama). dtype selects the
+// built by the layer-stack family (stack.cu: Matulorn, Dopilorn, Tosevik, Rumurax); a GGUF file names general.architecture (llama). dtype selects the
 // storage type of a folder model's matrices: "bfloat16" (default; bf16 weights, f32 accumulation) or "float32".
 extern "C" b200_model * b200_model_load_dtype(const char * path, int device, int layer_begin, int layer_end, const char * dtype) {
     try {

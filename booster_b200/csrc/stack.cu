@@ -1,9 +1,9 @@
 // stack.cu — the layer-stack model family on the B200 engine: configuration (config.json), weights (model.safetensors),
 // per-sequence state (attention cache + recurrent state), the step function for prompt portions and single tokens, and
-// the registry of designs and mixers. Kernels: stack_kernels.cuh. C-ABI dispatch: engine.cu.
+// the registry of designs and mixers. Kernels: stack_kernels.cuh, stack_kernels_mix.cuh, stack_kernels_hyper.cuh. C-ABI dispatch: engine.cu.
 //
 // A design is a name in config.json ("architecture") mapped to a builder that turns the configuration into a list of
-// LayerSpec; a mixer is a name ("type") mapped to a loader of its tensors and a forward routine. Three designs are registered:
+// LayerSpec; a mixer is a name ("type") mapped to a loader of its tensors and a forward routine. Four designs are registered:
 //   Matulorn   sequential sub-layers with grouped norms before and after each; mixers minGRU | latent attention (rotated
 //              part, window, sink) | gated delta rule; clamped gated feed-forward
 //   Dopilorn   both sub-layers read the same residual (x += mixer(n1 x) + ff(n2 x)) behind a causal convolution of their
@@ -155,6 +155,7 @@ struct StackModel {
     bool depth_avg = false;               // every layer hands on a weighted sum of all results so far
     bool has_pair = false;
     int streams = 1;                      // BLOCK_HYPER: copies of the residual
+    float final_g = 1.f;                  // BLOCK_HYPER: the model's norm weight (one number)
     bool rope_adjacent = false;           // the design rotates neighbouring pairs
     int vfirst_width = 0, vfirst_heads = 0;   // key/value heads x vdim, and key/value heads, of the first value-mixing layer (0: none so far)
     int max_slots = 0, max_eff = 0, max_exp = 0;      // routed mixtures: choices per token, expert width, experts
@@ -931,7 +932,7 @@ void build_rumurax(StackModel & m, const Json & cfg, const safetensors_file & sf
         m.weight_bytes = bytes0;
         add_run(m, i, -1);
     }
-    m.final_norm = up_f32(m, std::vector<float>((size_t) E, read_scalar(sf, "final.norm")));
+    m.final_g = read_scalar(sf, "final.norm");
     m.head = up_mat(m, sf.read_f32("head", {m.vocab, E}), m.vocab, E, nullptr);
 }
 
@@ -1097,7 +1098,7 @@ constexpr size_t ATT_SCORE_BYTES = (size_t) 256 << 20;
 void latent_values_out(StackCtx * c, const LayerSpec & L, int T, int ldp, int gate_off) {
     const int H = L.H, V = L.V, rank = L.rank;
     linear(c, c->OL, H * rank, L.uv, c->A, H * V, T, H, rank, V);
-    if (L.head_gate) { k_head_gate<<<T, 256, 0, c->st>>>(c->A, c->P + gate_off, ldp, H, V, L.gate_rows == H ? 0 : 1); c->launches++; }
+    if (L.head_gate) { k_head_gate<<<dim3((unsigned) T, T <= 16 ? (unsigned) ((H * V + 255) / 256) : 1u), 256, 0, c->st>>>(c->A, c->P + gate_off, ldp, H, V, L.gate_rows == H ? 0 : 1); c->launches++; }
     linear(c, c->A, H * V, L.o, c->out, c->m->E, T);
 }
 
@@ -1387,9 +1388,9 @@ void mixer_gqattn(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) {
     linear(c, c->in, E, L.proj, c->P, ldp, T);
     const GqaPrepArgs pa{c->P, ldp, H, G, D, V, L.qw, L.kw, c->m->eps, RopeArgs{L.rope_freq, L.rope_dims, 1.0f, L.rope_adjacent ? 1 : 0}, st, c->CV, cache, row,
                          c->VF, L.vmode, L.vlambda};
-    k_gqa_prep<<<T, 256, 0, c->st>>>(pa);
+    k_gqa_prep<<<dim3((unsigned) T, T <= 16 ? (unsigned) ((H + G + 7) / 8) : 1u), 256, 0, c->st>>>(pa);      // few tokens: a token's heads over several blocks
     c->launches++;
-    if (L.pool > 0) { k_pool_rows<<<T / L.pool + 1, 128, 0, c->st>>>(cache, row, pool, L.pool, st); c->launches++; }
+    if (L.pool > 0) { k_pool_rows<<<dim3((unsigned) (T / L.pool + 1), (unsigned) ((row + 127) / 128)), 128, 0, c->st>>>(cache, row, pool, L.pool, st); c->launches++; }
     const float * gate = L.head_gate ? c->P + nq + row : nullptr;
     const GqaMask mask{L.mask_kind, L.window, L.pool};
     const GqaScore sc{L.scale, L.cap};
@@ -1571,8 +1572,8 @@ void enqueue_layers_parallel(StackCtx * c, int T) {
 // shared unit's in c->Y; the layer's join weighs and adds them
 void mixture_ff(StackCtx * c, const LayerSpec & L, int T, const int32_t ** slot_of) {
     const int E = c->m->E, top = L.top, ff = L.e_ff, slots = T * top;
-    const RouteArgs ra{c->Hn, E, E, L.router, L.w_sg, L.n_exp, top, L.n_groups, L.keep_groups, L.r_scale, c->r_sel, c->r_wt, c->r_sg, c->r_z, c->r_counter, L.route_fn};
-    k_moe_route<<<dim3((unsigned) T, (unsigned) ((L.n_exp + (L.w_sg ? 1 : 0) + 7) / 8)), 256, (size_t) (2 * L.n_exp + L.n_groups) * 4, c->st>>>(ra);
+    const RouteArgs ra{c->Hn, E, E, L.router, L.w_sg, L.n_exp, top, L.n_groups, L.keep_groups, L.r_scale, c->r_sel, c->r_wt, c->r_sg, c->r_z, c->r_counter, L.route_fn, T <= 16 ? 8 : 1};
+    k_moe_route<<<dim3((unsigned) T, (unsigned) ((L.n_exp + (L.w_sg ? 1 : 0) + 8 / ra.wpr - 1) / (8 / ra.wpr))), 256, (size_t) (2 * L.n_exp + L.n_groups) * 4, c->st>>>(ra);
     c->launches++;
     LinOpt o;
     o.alpha = 1.f; o.shift = 0.f;               // silu(gate) * up, no clamp
@@ -1653,30 +1654,31 @@ void enqueue_layers_prenorm(StackCtx * c, int T) {
 }
 
 // hyper-connected blocks: the residual is m.streams rows per token; every sub-layer ends in one k_hc_join launch that writes all
-// streams and norms the read-in of the sub-layer that follows. c->X gets the sum of the streams where it is wanted (taps, the head).
+// streams and norms the read-in of the sub-layer that follows; the last one leaves the model's norm of the sum of the streams in
+// c->Hn for the head. c->X gets the sum of the streams when the residual after a layer is tapped.
 void enqueue_layers_hyper(StackCtx * c, int T) {
     StackModel & m = *c->m;
     const int E = m.E, S = m.streams;
     const long long plane = (long long) c->cap * E;
     {
         const LayerSpec & L0 = m.layers[(size_t) m.runs[0].layer];
-        if (m.dtype == STACK_F32) k_hc_embed<float><<<T, 256, 0, c->st>>>((const float *) m.embed, c->d_step->tokens, E, m.vocab, S, c->XS, plane, L0.hc[0], L0.g1, m.eps, c->Hn);
-        else k_hc_embed<__nv_bfloat16><<<T, 256, 0, c->st>>>((const __nv_bfloat16 *) m.embed, c->d_step->tokens, E, m.vocab, S, c->XS, plane, L0.hc[0], L0.g1, m.eps, c->Hn);
+        if (m.dtype == STACK_F32) k_hc_embed<float><<<T, hc_threads(T, E), 0, c->st>>>((const float *) m.embed, c->d_step->tokens, E, m.vocab, S, c->XS, plane, L0.hc[0], L0.g1, m.eps, c->Hn);
+        else k_hc_embed<__nv_bfloat16><<<T, hc_threads(T, E), 0, c->st>>>((const __nv_bfloat16 *) m.embed, c->d_step->tokens, E, m.vocab, S, c->XS, plane, L0.hc[0], L0.g1, m.eps, c->Hn);
         c->launches++;
     }
     for (size_t ri = 0; ri < m.runs.size(); ri++) {
         const RunSpec & R = m.runs[ri];
         const LayerSpec & L = m.layers[(size_t) R.layer];
         const LayerSpec * N = ri + 1 < m.runs.size() ? &m.layers[(size_t) m.runs[ri + 1].layer] : nullptr;      // the final norm runs on the wanted rows only
-        const bool want_sum = c->taps || !N;
         const auto join = [&](int q, HcJoinArgs & j) {
             j.XS = c->XS; j.plane = plane; j.S = S; j.E = E; j.eps = m.eps;
             j.w = L.hc[q];
             const bool last_sub = q == 1 || !L.has_mlp;
             const HcW * nw = !last_sub ? &L.hc[1] : N ? &N->hc[0] : nullptr;
             if (nw) { for (int s = 0; s < HC_MAX; s++) j.nin[s] = nw->in[s]; j.g = !last_sub ? L.g2 : N->g1; j.Hn = c->Hn; }
-            if (last_sub && want_sum) j.Xsum = c->X;
-            k_hc_join<<<T, 256, 0, c->st>>>(j);
+            else { for (int s = 0; s < S; s++) j.nin[s] = 1.f; j.g = m.final_g; j.Hn = c->Hn; }      // after the last layer: the model's norm of the sum of the streams
+            if (last_sub && c->taps) j.Xsum = c->X;
+            k_hc_join<<<T, hc_threads(T, E), 0, c->st>>>(j);
             c->launches++;
         };
         c->in = c->Hn; c->out = c->Y;
@@ -1705,8 +1707,15 @@ void enqueue_layers(StackCtx * c, int T) {
 }
 
 // final norm + head on n_rows rows of the pass (row indices in d_step->rows) -> d_logits[row_off ..]
-void enqueue_head(StackCtx * c, int n_rows, int64_t row_off) {
+void enqueue_head(StackCtx * c, int n_rows, int64_t row_off, bool one_token = false) {
     StackModel & m = *c->m;
+    if (m.block == BLOCK_HYPER) {
+        // the last join left the normed sum of the streams in Hn for every row of the pass: the wanted rows are gathered for the head
+        const float * hn = c->Hn;
+        if (!one_token) { k_gather_rows<<<n_rows, 128, 0, c->st>>>(c->Hn, m.E, c->d_step->rows, m.E, c->Y); c->launches++; hn = c->Y; }
+        linear(c, hn, m.E, m.head, c->d_logits + row_off * m.vocab, m.vocab, n_rows);
+        return;
+    }
     if (m.dyt) { k_dyt_rows<<<n_rows, 256, 0, c->st>>>(c->X, m.E, c->d_step->rows, DytW{m.final_norm, m.final_b, m.final_alpha}, m.E, c->Hn, m.E); c->launches++; }
     else norm(c, c->X, m.E, c->d_step->rows, m.final_norm, m.E, m.groups, c->Hn, m.E, n_rows, false);
     linear(c, c->Hn, m.E, m.head, c->d_logits + row_off * m.vocab, m.vocab, n_rows);
@@ -1742,7 +1751,7 @@ void enqueue_token_step(StackCtx * c) {
     SCU(cudaMemcpyAsync(c->d_step, c->h_step, sizeof(StepState) + sizeof(int32_t), cudaMemcpyHostToDevice, c->st));
     SCU(cudaMemsetAsync(c->d_step->rows, 0, sizeof(int32_t), c->st));      // the wanted row is the token itself (a prompt pass leaves its own rows here)
     enqueue_layers(c, 1);
-    enqueue_head(c, 1, 0);
+    enqueue_head(c, 1, 0, true);
     SCU(cudaMemcpyAsync(c->h_logits, c->d_logits, (size_t) c->m->vocab * 4, cudaMemcpyDeviceToHost, c->st));
 }
 
@@ -2055,7 +2064,7 @@ void stack_generate_greedy(StackCtx * c, int32_t first_token, int pos0, int n_st
     c->h_step->st.pos0 = pos0; c->h_step->st.n_tokens = 1; c->h_step->tokens[0] = first_token;
     const auto body = [&]() {
         enqueue_layers(c, 1);
-        enqueue_head(c, 1, 0);
+        enqueue_head(c, 1, 0, true);
         k_argmax_advance<<<1, 1024, 0, c->st>>>(c->d_logits, m.vocab, &c->d_step->st, c->d_step->tokens, c->d_out_tokens, c->d_counter);
         c->launches++;
     };

@@ -1,7 +1,8 @@
 // stack.hpp — host interface of the layer-stack model family (stack.cu): models described by a config.json whose
 // "layers" list names, per layer, a mixer (minGRU | latent attention | gated delta rule | generalized delta rule |
-// differential sliding-window attention | retention | a sigmoid attention beside a retention) and an optional feed-forward
-// (gated unit | polynomial | routed mixture of gated units); three designs (Matulorn, Dopilorn, Tosevik) arrange them.
+// differential sliding-window attention | retention | a sigmoid attention beside a retention | soft-max attention over grouped
+// heads under a chunk mask or a window with block means) and an optional feed-forward (gated unit | polynomial | routed mixture
+// of gated units); four designs (Matulorn, Dopilorn, Tosevik, Rumurax) arrange them.
 // engine.cu dispatches the C-ABI (b200_model_load, b200_ctx_new, b200_decode, ...) here when the model path is a folder
 // with config.json + model.safetensors; the GGUF LLaMA path stays where it was. Functions throw std::runtime_error.
 #pragma once

@@ -1568,10 +1568,10 @@ __global__ void __launch_bounds__(256) k_polynorm(float * __restrict__ Z, int n,
 
 // ---- small element-wise steps ---------------------------------------------------------------------------------------------------
 // output gate: A[t][h][0..V) *= sigmoid(gate[t][h]) (one number per head), or with per_entry = 1 A[t][i] *= sigmoid(gate[t][i])
-// (one number per entry); gate rows of stride ldg
+// (one number per entry); gate rows of stride ldg. grid (T, slices of a row)
 __global__ void k_head_gate(float * __restrict__ A, const float * __restrict__ gate, int ldg, int H, int V, int per_entry) {
     const int t = blockIdx.x;
-    for (int i = threadIdx.x; i < H * V; i += blockDim.x) A[(size_t) t * H * V + i] *= sigmoidf_(gate[(size_t) t * ldg + (per_entry ? i : i / V)]);
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H * V; i += blockDim.x * gridDim.y) A[(size_t) t * H * V + i] *= sigmoidf_(gate[(size_t) t * ldg + (per_entry ? i : i / V)]);
 }
 // soft cap on the logits: x <- cap tanh(x / cap)
 __global__ void k_softcap(float * __restrict__ x, size_t n, float cap) {

@@ -19,47 +19,51 @@ struct HcW {                           // one sub-layer's connection weights
     float out[HC_MAX];
 };
 
-// sum over a block of 256 threads; every thread gets the total. red: 8 floats of shared memory
-__device__ __forceinline__ float block_sum_256(float v, float * red) {
+// sum over a block of up to 1024 threads (a multiple of 32); every thread gets the total. red: 32 floats of shared memory
+__device__ __forceinline__ float block_sum(float v, float * red) {
     v = warp_sum(v);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
     __syncthreads();
     float t = 0.f;
-#pragma unroll
-    for (int w = 0; w < 8; w++) t += red[w];
+    const int nw = blockDim.x >> 5;
+    for (int w = 0; w < nw; w++) t += red[w];
     __syncthreads();
     return t;
 }
+// threads per row of the stream kernels: steps of few tokens spread a row over a whole block (two entries per thread), so that
+// the loads of a row are in flight together; prompt portions have rows enough to fill the SMs with smaller blocks
+inline int hc_threads(int T, int E) { return T > 16 ? 256 : (E / 2 + 31) / 32 * 32 < 128 ? 128 : (E / 2 + 31) / 32 * 32 > 1024 ? 1024 : (E / 2 + 31) / 32 * 32; }
 
 // embedding into all S streams, fused with the first sub-layer's read-in and norm:
 // XS[s][t] = embed[token[t]]; Hn[t] = u / sqrt(mean(u^2) + eps) * g with u = sum_s in[s] XS[s][t]
 template <typename WT>
-__global__ void __launch_bounds__(256) k_hc_embed(const WT * __restrict__ embed, const int32_t * __restrict__ tokens, int E, int n_vocab, int S,
+__global__ void __launch_bounds__(1024) k_hc_embed(const WT * __restrict__ embed, const int32_t * __restrict__ tokens, int E, int n_vocab, int S,
                                                   float * __restrict__ XS, long long plane, HcW w, float g, float eps, float * __restrict__ Hn) {
-    __shared__ float red[8];
-    const int t = blockIdx.x;
+    __shared__ float red[32];
+    const int t = blockIdx.x, nt = blockDim.x;
     int tok = tokens[t];
     tok = tok < 0 ? 0 : tok >= n_vocab ? n_vocab - 1 : tok;      // ids are validated on the host; never read outside the table
     const size_t row = (size_t) t * E;
     float a = 0.f;
     for (int s = 0; s < S; s++) a += w.in[s];
     float ss = 0.f;
-    for (int i = threadIdx.x; i < E; i += 256) {
+    for (int i = threadIdx.x; i < E; i += nt) {
         const float x = wf(embed, (size_t) tok * E + i);
         for (int s = 0; s < S; s++) XS[(size_t) s * plane + row + i] = x;
         const float u = a * x;
         Hn[row + i] = u;
         ss = fmaf(u, u, ss);
     }
-    ss = block_sum_256(ss, red);
+    ss = block_sum(ss, red);
     const float r = g / sqrtf(ss / (float) E + eps);
-    for (int i = threadIdx.x; i < E; i += 256) Hn[row + i] *= r;
+    for (int i = threadIdx.x; i < E; i += nt) Hn[row + i] *= r;
 }
 
 // end of a sub-layer: all streams at once from the old ones, x_t <- sum_s mix[s][t] x_s + out[t] y, where y is the sub-layer's
 // output: Ya[t] (may be nullptr) plus, for a routed mixture, the chosen experts' outputs Yk[slot(t, k)], k < top, as they are
 // (slot_of == nullptr: slot t top + k). Then, for the sub-layer that follows, u = sum_t nin[t] x_t and Hn[t] = u / rms(u) * g
-// (Hn == nullptr: nothing follows), and Xsum[t] = sum_t x_t when the residual itself is wanted. One block per token.
+// (Hn == nullptr: nothing follows), and Xsum[t] = sum_t x_t when the residual itself is wanted. One block per token
+// (hc_threads threads).
 struct HcJoinArgs {
     float * XS; long long plane; int S, E;
     const float * Ya;
@@ -68,12 +72,15 @@ struct HcJoinArgs {
     float nin[HC_MAX]; float g; float eps; float * Hn;
     float * Xsum;
 };
-__global__ void __launch_bounds__(256) k_hc_join(const HcJoinArgs a) {
-    __shared__ float red[8];
-    const int t = blockIdx.x, S = a.S;
+constexpr int HC_OWN = 4;              // read-in entries a thread keeps in registers until the row's sum of squares is known
+__global__ void __launch_bounds__(1024) k_hc_join(const HcJoinArgs a) {
+    __shared__ float red[32];
+    const int t = blockIdx.x, S = a.S, nt = blockDim.x;
     const size_t row = (size_t) t * a.E;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < a.E; i += 256) {
+    const bool own = a.E <= HC_OWN * nt;
+    float ss = 0.f, keep[HC_OWN];
+    int n_own = 0;
+    for (int i = threadIdx.x; i < a.E; i += nt) {
         float y = a.Ya ? a.Ya[row + i] : 0.f;
         if (a.Yk) for (int k = 0; k < a.top; k++) {
             const int s = t * a.top + k;
@@ -95,12 +102,22 @@ __global__ void __launch_bounds__(256) k_hc_join(const HcJoinArgs a) {
             }
         }
         if (a.Xsum) a.Xsum[row + i] = sum;
-        if (a.Hn) { a.Hn[row + i] = u; ss = fmaf(u, u, ss); }
+        if (a.Hn) {
+            ss = fmaf(u, u, ss);
+            if (own) {
+#pragma unroll
+                for (int k = 0; k < HC_OWN; k++) if (k == n_own) keep[k] = u;
+                n_own++;
+            } else a.Hn[row + i] = u;
+        }
     }
     if (!a.Hn) return;
-    ss = block_sum_256(ss, red);
+    ss = block_sum(ss, red);
     const float r = a.g / sqrtf(ss / (float) a.E + a.eps);
-    for (int i = threadIdx.x; i < a.E; i += 256) a.Hn[row + i] *= r;
+    if (own) {
+#pragma unroll
+        for (int k = 0; k < HC_OWN; k++) if (k < n_own) a.Hn[row + threadIdx.x + (size_t) k * nt] = keep[k] * r;
+    } else for (int i = threadIdx.x; i < a.E; i += nt) a.Hn[row + i] *= r;
 }
 
 // ---- soft-max attention over grouped key/value heads ------------------------------------------------------------------------------
@@ -109,7 +126,7 @@ __global__ void __launch_bounds__(256) k_hc_join(const HcJoinArgs a) {
 // (qw / kw; nullptr: no norm), then the rotation of the first rope.dims entries by the token's position. Queries go to Q[t]
 // (H x D), keys and values to the cache row of the position: [ k: G x D | v: G x V ]. Values: vmode 1 also leaves them in
 // vfirst[t] (the first mixing layer of the model); vmode 2 stores (1 - lambda) v + lambda vfirst[t] (a later mixing layer; the
-// mixed values are what the cache keeps). One block per token, a warp per head.
+// mixed values are what the cache keeps). grid (T, blocks): a warp per head, the heads and the value entries dealt over the blocks of a token.
 enum { GQA_V_PLAIN = 0, GQA_V_FIRST = 1, GQA_V_MIX = 2 };
 struct GqaPrepArgs {
     const float * P; int ldp;
@@ -126,7 +143,8 @@ __global__ void __launch_bounds__(256) k_gqa_prep(const GqaPrepArgs a) {
     const float * q = a.P + (size_t) t * a.ldp, * k = q + nq, * v = k + nk;
     float * row = a.cache + (size_t) pos * a.ldc;
     const int half = a.rope.dims / 2;
-    for (int vec = warp; vec < a.H + a.G; vec += 8) {
+    const int nblk = gridDim.y, bk = blockIdx.y;
+    for (int vec = bk * 8 + warp; vec < a.H + a.G; vec += 8 * nblk) {
         const bool is_q = vec < a.H;
         const float * src = is_q ? q + (size_t) vec * a.D : k + (size_t) (vec - a.H) * a.D;
         const float * w = is_q ? a.qw : a.kw;
@@ -147,7 +165,7 @@ __global__ void __launch_bounds__(256) k_gqa_prep(const GqaPrepArgs a) {
         }
         for (int i = a.rope.dims + lane; i < a.D; i += 32) dst[i] = w ? src[i] * r * w[i] : src[i];
     }
-    for (int i = tid; i < nv; i += 256) {
+    for (int i = bk * 256 + tid; i < nv; i += 256 * nblk) {
         float x = v[i];
         if (a.vmode == GQA_V_MIX) x = fmaf(a.lambda, a.vfirst[(size_t) t * nv + i], (1.0f - a.lambda) * x);
         else if (a.vmode == GQA_V_FIRST) a.vfirst[(size_t) t * nv + i] = x;
@@ -156,12 +174,12 @@ __global__ void __launch_bounds__(256) k_gqa_prep(const GqaPrepArgs a) {
 }
 
 // means of whole blocks of P cached rows: pool[b] = (1 / P) sum_(j < P) cache[b P + j], for every block whose last position
-// b P + P - 1 lies in this step (its rows are all in the cache then). grid: n_tokens / P + 1 blocks.
+// b P + P - 1 lies in this step (its rows are all in the cache then). grid (n_tokens / P + 1, slices of the row).
 __global__ void k_pool_rows(const float * __restrict__ cache, int ldc, float * __restrict__ pool, int P, const StepState * __restrict__ st) {
     const int b = st->pos0 / P + blockIdx.x;
     if ((long long) (b + 1) * P > (long long) st->pos0 + st->n_tokens) return;
     const float * src = cache + (size_t) b * P * ldc;
-    for (int i = threadIdx.x; i < ldc; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < ldc; i += blockDim.x * gridDim.y) {
         float s = 0.f;
         for (int j = 0; j < P; j++) s += src[(size_t) j * ldc + i];
         pool[(size_t) b * ldc + i] = s / (float) P;
@@ -234,6 +252,10 @@ __global__ void __launch_bounds__(256) k_gqa_attn(const GqaAttnArgs a) {
             float s = -INFINITY;
             if (lane < cnt) {
                 const float * k1 = (n < nb ? a.pool + (size_t) n * a.ldc : tokens + (long long) n * a.ldc) + koff;
+                // the lane's key row and value row are asked for now, whole: the dot product and the weighted sum then find them in L2
+                const char * kp = reinterpret_cast<const char *>(k1), * vp = reinterpret_cast<const char *>(k1 - koff + voff);
+                for (int b = 128; b < a.D * 4; b += 128) asm volatile("prefetch.global.L2 [%0];" :: "l"(kp + b));
+                for (int b = 0; b < a.V * 4; b += 128) asm volatile("prefetch.global.L2 [%0];" :: "l"(vp + b));
                 float x0 = 0.f, x1 = 0.f;
                 if (a.vec) {
 #pragma unroll 8
@@ -254,7 +276,7 @@ __global__ void __launch_bounds__(256) k_gqa_attn(const GqaAttnArgs a) {
 #pragma unroll
             for (int i = 0; i < VPL; i++) acc[i] *= corr;
             m = mn;
-#pragma unroll 4
+#pragma unroll 8
             for (int kk = 0; kk < cnt; kk++) {
                 const float wk = __shfl_sync(0xffffffffu, w, kk);
                 const int nn = nbase + kk;

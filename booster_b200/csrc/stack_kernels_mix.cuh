@@ -620,7 +620,8 @@ __global__ void k_group_o_layout(const float * __restrict__ Or, int Tpad, int H,
 // of equal size; a block ranks by the best s inside it and the choice is confined to the `keep` best-ranked blocks: of their experts
 // the `top` with the largest s are taken (lowest index first among equals), each weighing in with s * scale as it is.
 // sel[t][top], wt[t][top]; sg[t] = sigmoid(w_sg . h) is the shared unit's gate (w_sg == nullptr: no shared unit).
-// grid (T, ceil(rows / 8)) with rows = n (+ 1 for the shared gate): a warp per row of the router, several 16-byte loads in flight;
+// grid (T, ceil(rows / (8 / wpr))) with rows = n (+ 1 for the shared gate): wpr warps per row of the router (1, or 8 for steps of few
+// tokens, whose rows would otherwise be walked by one warp each), several 16-byte loads in flight;
 // the logits go to z[t][n + 1], and the block of a token that finishes last (an atomic counter, no waiting) makes the choice with
 // one warp. Dynamic shared memory: 2 n + n_groups floats.
 struct RouteArgs {
@@ -631,6 +632,7 @@ struct RouteArgs {
     int32_t * sel; float * wt; float * sg;
     float * z; int * counter;
     int score_fn;       // 0: soft-max over the experts; 1: sigmoid of each logit
+    int wpr;            // warps per router row: 1 (a block takes 8 rows) or 8 (a block takes one row, each warp an eighth of it: steps of few tokens)
 };
 __global__ void __launch_bounds__(256) k_moe_route(const RouteArgs a) {
     extern __shared__ float rsm[];
@@ -638,22 +640,30 @@ __global__ void __launch_bounds__(256) k_moe_route(const RouteArgs a) {
     float * s = rsm, * elig = rsm + a.n, * gbest = rsm + 2 * a.n;
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float * h = a.Hn + (size_t) t * a.ld;
-    const int rows = a.n + (a.w_sg ? 1 : 0), e = blockIdx.y * 8 + warp;
+    __shared__ float psum[8];
+    const int wpr = a.wpr, kw = warp % wpr;
+    const int rows = a.n + (a.w_sg ? 1 : 0), e = blockIdx.y * (8 / wpr) + warp / wpr;
     float * z = a.z + (size_t) t * (a.n + 1);
     if (e < rows) {
         const float * w = e < a.n ? a.Wr + (size_t) e * a.E : a.w_sg;
         float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
         if ((a.E & 3) == 0 && (a.ld & 3) == 0 && (((uintptr_t) w | (uintptr_t) h) & 15) == 0) {
 #pragma unroll 4
-            for (int i = lane * 4; i < a.E; i += 128) {
+            for (int i = (kw * 32 + lane) * 4; i < a.E; i += 128 * wpr) {
                 const float4 x = *reinterpret_cast<const float4 *>(h + i), y = __ldg(reinterpret_cast<const float4 *>(w + i));
                 acc0 = fmaf(x.x, y.x, acc0); acc1 = fmaf(x.y, y.y, acc1); acc2 = fmaf(x.z, y.z, acc2); acc3 = fmaf(x.w, y.w, acc3);
             }
         } else {
-            for (int i = lane; i < a.E; i += 32) acc0 = fmaf(w[i], h[i], acc0);
+            for (int i = kw * 32 + lane; i < a.E; i += 32 * wpr) acc0 = fmaf(w[i], h[i], acc0);
         }
-        const float acc = warp_sum((acc0 + acc1) + (acc2 + acc3));
-        if (lane == 0) { if (e < a.n) z[e] = acc; else a.sg[t] = sigmoidf_(acc); }
+        float acc = warp_sum((acc0 + acc1) + (acc2 + acc3));
+        if (wpr > 1) {                                      // the row's warps: partial sums through shared memory, in a fixed order
+            if (lane == 0) psum[warp] = acc;
+            __syncthreads();
+            acc = 0.f;
+            for (int k = 0; k < wpr; k++) acc += psum[k];
+        }
+        if (lane == 0 && kw == 0) { if (e < a.n) z[e] = acc; else a.sg[t] = sigmoidf_(acc); }
     }
     if (gridDim.y > 1) {
         __threadfence();

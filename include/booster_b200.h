@@ -47,8 +47,8 @@ const char * b200_version(void);
  *                     f16 KV cache for the stage's layers (:2926-3022), n_ctx padded to 32 (:16655).            */
 b200_model * b200_model_load(const char * gguf_path, int device, int layer_begin, int layer_end);
 /* Model registry by container. A path that is a folder holding config.json + model.safetensors (or that config.json itself)
- * is a model of the layer-stack family: config.json names the design in "architecture" (registered: "Matulorn", "Dopilorn", "Tosevik") and
- * lists the layers, each one mixer ("mingru", "latent_attention", "delta", "general_delta", "attention", "retention", "parallel";
+ * is a model of the layer-stack family: config.json names the design in "architecture" (registered: "Matulorn", "Dopilorn", "Tosevik", "Rumurax") and
+ * lists the layers, each one mixer ("mingru", "latent_attention", "delta", "general_delta", "attention", "attention_2", "retention", "parallel";
  * a design admits its own) and an optional feed-forward. dtype = "bfloat16"
  * (default when NULL: matrices stay bfloat16, 32-bit accumulation; norms, recurrences, attention weights and the residual
  * stream in float32) or "float32" (everything in true 32-bit on the CUDA cores). b200_model_load on such a path uses the
