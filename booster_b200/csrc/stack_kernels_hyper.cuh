@@ -232,6 +232,7 @@ __global__ void __launch_bounds__(256) k_gqa_attn(const GqaAttnArgs a) {
     constexpr int MGW = 2 + 32 * VPL;
     float * qs = sm;                                        // [TQ][D]
     float * mg = sm + (size_t) a.TQ * a.D;                  // [8 warps][MGW]
+    const int pos0 = a.st->pos0;                            // asked for together with the queries: one round trip, not two
     for (int i = tid; i < a.TQ * a.D; i += 256) {
         const int q = i / a.D, e = i - q * a.D;
         qs[i] = t0 + q < a.T ? a.Q[(size_t) (t0 + q) * a.ldq + (size_t) h * a.D + e] : 0.f;
@@ -241,7 +242,7 @@ __global__ void __launch_bounds__(256) k_gqa_attn(const GqaAttnArgs a) {
 #pragma unroll
     for (int i = 0; i < VPL; i++) acc[i] = 0.f;
     if (t < a.T) {
-        const int p = a.st->pos0 + t;
+        const int p = pos0 + t;
         const int jlo = gqa_first_token(a.mask, p), nb = gqa_blocks_seen(a.mask, p), ntot = nb + p - jlo + 1;
         const float * q1 = qs + (size_t) qi * a.D;
         const float r1 = a.r1 ? a.r1[h] : 0.f, r2 = a.r1 ? a.r2[h] : 0.f;
