@@ -1678,7 +1678,8 @@ void enqueue_layers_hyper(StackCtx * c, int T) {
             if (nw) { for (int s = 0; s < HC_MAX; s++) j.nin[s] = nw->in[s]; j.g = !last_sub ? L.g2 : N->g1; j.Hn = c->Hn; }
             else { for (int s = 0; s < S; s++) j.nin[s] = 1.f; j.g = m.final_g; j.Hn = c->Hn; }      // after the last layer: the model's norm of the sum of the streams
             if (last_sub && c->taps) j.Xsum = c->X;
-            k_hc_join<<<T, hc_threads(T, E), 0, c->st>>>(j);
+            if (E % 4 == 0) k_hc_join<4><<<T, hc_threads(T, E, 4, 512), 0, c->st>>>(j);      // every buffer of a context is 16-byte aligned and its rows are E floats apart
+            else k_hc_join<1><<<T, hc_threads(T, E), 0, c->st>>>(j);
             c->launches++;
         };
         c->in = c->Hn; c->out = c->Y;

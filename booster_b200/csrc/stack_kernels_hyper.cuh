@@ -30,9 +30,12 @@ __device__ __forceinline__ float block_sum(float v, float * red) {
     __syncthreads();
     return t;
 }
-// threads per row of the stream kernels: steps of few tokens spread a row over a whole block (two entries per thread), so that
-// the loads of a row are in flight together; prompt portions have rows enough to fill the SMs with smaller blocks
-inline int hc_threads(int T, int E) { return T > 16 ? 256 : (E / 2 + 31) / 32 * 32 < 128 ? 128 : (E / 2 + 31) / 32 * 32 > 1024 ? 1024 : (E / 2 + 31) / 32 * 32; }
+// threads per row of the stream kernels: steps of few tokens spread a row over a whole block (`per_thread` entries per thread), so
+// that the loads of a row are in flight together; prompt portions have rows enough to fill the SMs with smaller blocks
+inline int hc_threads(int T, int E, int per_thread = 2, int most = 1024) {
+    const int n = (E / per_thread + 31) / 32 * 32;
+    return T > 16 ? 256 : n < 128 ? 128 : n > most ? most : n;
+}
 
 // embedding into all S streams, fused with the first sub-layer's read-in and norm:
 // XS[s][t] = embed[token[t]]; Hn[t] = u / sqrt(mean(u^2) + eps) * g with u = sum_s in[s] XS[s][t]
@@ -72,43 +75,69 @@ struct HcJoinArgs {
     float nin[HC_MAX]; float g; float eps; float * Hn;
     float * Xsum;
 };
-constexpr int HC_OWN = 4;              // read-in entries a thread keeps in registers until the row's sum of squares is known
-__global__ void __launch_bounds__(1024) k_hc_join(const HcJoinArgs a) {
+// VEC = 4: rows are walked in 16-byte chunks (E a multiple of 4, 16-byte aligned rows); VEC = 1: any E.
+template <int VEC> __device__ __forceinline__ void ld_chunk(const float * p, float (&v)[VEC]) {
+    if constexpr (VEC == 4) { const float4 f = *reinterpret_cast<const float4 *>(p); v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w; }
+    else v[0] = p[0];
+}
+template <int VEC> __device__ __forceinline__ void st_chunk(float * p, const float (&v)[VEC]) {
+    if constexpr (VEC == 4) *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    else p[0] = v[0];
+}
+constexpr int HC_OWN = 2;              // read-in chunks a thread keeps in registers until the row's sum of squares is known
+template <int VEC>
+__global__ void __launch_bounds__(VEC == 4 ? 512 : 1024) k_hc_join(const HcJoinArgs a) {
     __shared__ float red[32];
-    const int t = blockIdx.x, S = a.S, nt = blockDim.x;
+    const int t = blockIdx.x, S = a.S, nt = blockDim.x, nchunk = a.E / VEC;
     const size_t row = (size_t) t * a.E;
-    const bool own = a.E <= HC_OWN * nt;
-    float ss = 0.f, keep[HC_OWN];
+    const bool own = nchunk <= HC_OWN * nt;
+    float ss = 0.f, keep[HC_OWN][VEC];
     int n_own = 0;
-    for (int i = threadIdx.x; i < a.E; i += nt) {
-        float y = a.Ya ? a.Ya[row + i] : 0.f;
-        if (a.Yk) for (int k = 0; k < a.top; k++) {
-            const int s = t * a.top + k;
-            y += a.Yk[(size_t) (a.slot_of ? a.slot_of[s] : s) * a.E + i];
-        }
-        float old[HC_MAX];
+    for (int c = threadIdx.x; c < nchunk; c += nt) {
+        const int i = c * VEC;
+        float y[VEC], old[HC_MAX][VEC];
 #pragma unroll
-        for (int s = 0; s < HC_MAX; s++) old[s] = s < S ? a.XS[(size_t) s * a.plane + row + i] : 0.f;
-        float u = 0.f, sum = 0.f;
+        for (int e = 0; e < VEC; e++) y[e] = 0.f;
+        if (a.Ya) ld_chunk<VEC>(a.Ya + row + i, y);
+#pragma unroll
+        for (int s = 0; s < HC_MAX; s++) if (s < S) ld_chunk<VEC>(a.XS + (size_t) s * a.plane + row + i, old[s]);
+        if (a.Yk) for (int k = 0; k < a.top; k++) {
+            const int sl = t * a.top + k;
+            float v[VEC];
+            ld_chunk<VEC>(a.Yk + (size_t) (a.slot_of ? a.slot_of[sl] : sl) * a.E + i, v);
+#pragma unroll
+            for (int e = 0; e < VEC; e++) y[e] += v[e];
+        }
+        float u[VEC], sum[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; e++) u[e] = sum[e] = 0.f;
 #pragma unroll
         for (int q = 0; q < HC_MAX; q++) {
             if (q < S) {
-                float v = a.w.out[q] * y;
+                float v[VEC];
 #pragma unroll
-                for (int s = 0; s < HC_MAX; s++) if (s < S) v = fmaf(a.w.mix[s * S + q], old[s], v);
-                a.XS[(size_t) q * a.plane + row + i] = v;
-                u = fmaf(a.nin[q], v, u);
-                sum += v;
+                for (int e = 0; e < VEC; e++) {
+                    v[e] = a.w.out[q] * y[e];
+#pragma unroll
+                    for (int s = 0; s < HC_MAX; s++) if (s < S) v[e] = fmaf(a.w.mix[s * S + q], old[s][e], v[e]);
+                    u[e] = fmaf(a.nin[q], v[e], u[e]);
+                    sum[e] += v[e];
+                }
+                st_chunk<VEC>(a.XS + (size_t) q * a.plane + row + i, v);
             }
         }
-        if (a.Xsum) a.Xsum[row + i] = sum;
+        if (a.Xsum) st_chunk<VEC>(a.Xsum + row + i, sum);
         if (a.Hn) {
-            ss = fmaf(u, u, ss);
+#pragma unroll
+            for (int e = 0; e < VEC; e++) ss = fmaf(u[e], u[e], ss);
             if (own) {
 #pragma unroll
-                for (int k = 0; k < HC_OWN; k++) if (k == n_own) keep[k] = u;
+                for (int k = 0; k < HC_OWN; k++) if (k == n_own) {
+#pragma unroll
+                    for (int e = 0; e < VEC; e++) keep[k][e] = u[e];
+                }
                 n_own++;
-            } else a.Hn[row + i] = u;
+            } else st_chunk<VEC>(a.Hn + row + i, u);
         }
     }
     if (!a.Hn) return;
@@ -116,7 +145,12 @@ __global__ void __launch_bounds__(1024) k_hc_join(const HcJoinArgs a) {
     const float r = a.g / sqrtf(ss / (float) a.E + a.eps);
     if (own) {
 #pragma unroll
-        for (int k = 0; k < HC_OWN; k++) if (k < n_own) a.Hn[row + threadIdx.x + (size_t) k * nt] = keep[k] * r;
+        for (int k = 0; k < HC_OWN; k++) if (k < n_own) {
+            float v[VEC];
+#pragma unroll
+            for (int e = 0; e < VEC; e++) v[e] = keep[k][e] * r;
+            st_chunk<VEC>(a.Hn + row + ((size_t) threadIdx.x + (size_t) k * nt) * VEC, v);
+        }
     } else for (int i = threadIdx.x; i < a.E; i += nt) a.Hn[row + i] *= r;
 }
 

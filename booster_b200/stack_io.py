@@ -79,7 +79,7 @@ def tosevik_config(width: int, n_layer: int, ff: int, heads: int, vocab: int = 3
 
 def rumurax_config(width: int, n_layer: int, ff: int, heads: int, vocab: int = 32000, head_dim: int = 128, kv_heads: int = 0, experts: int = 16, top: int = 4,
                    streams: int = 4, window: int = 1024, pool: int = 32, chunk: int = 1024, kv_rank: int = 512, rot_dim: int = 64,
-                   pattern=("attention_2", "attention", "latent_attention", "attention")) -> dict:
+                   pattern=("attention", "attention_2", "attention", "latent_attention")) -> dict:
     """a Rumurax configuration whose layers resemble a real model's: mixers in `pattern` order, a routed mixture on every layer whose
     chosen experts plus the shared unit are as wide together as a dense feed-forward of `ff` (top x 3 ff / 16 + ff / 4)"""
     e_ff = max(8, ff * 3 // (4 * top) // 8 * 8)
