@@ -1112,12 +1112,12 @@ void mixer_latent(StackCtx * c, const LayerSpec & L, const RunSpec & Rn, int T) 
     if (L.q_rank > 0) {
         // P[t] = [ query latent | down-projection | head gates ]: norm of the query latent in place, q = W_uq c_q into A, cache row, absorbed queries from A
         gate_off = L.q_rank + rank;
-        k_latent_prep<<<T, 128, 0, c->st>>>(c->P, ldp, H, D, 0, rank, L.cnorm, c->m->eps, rope, &c->d_step->st, cache, c->QK, L.q_rank, L.qnorm, L.q_rank);
+        k_latent_prep<<<dim3((unsigned) T, T <= 16 ? (unsigned) ((H + 4) / 4) : 1u), 128, 0, c->st>>>(c->P, ldp, H, D, 0, rank, L.cnorm, c->m->eps, rope, &c->d_step->st, cache, c->QK, L.q_rank, L.qnorm, L.q_rank);
         linear(c, c->P, ldp, L.uq, c->A, H * D, T);
         linear(c, c->A, H * D, L.ukT, c->QK, H * W, T, H, D, W);
     } else {
         gate_off = H * (D + R) + W;
-        k_latent_prep<<<T, 128, 0, c->st>>>(c->P, ldp, H, D, R, rank, L.cnorm, c->m->eps, rope, &c->d_step->st, cache, c->QK, H * (D + R), nullptr, 0);
+        k_latent_prep<<<dim3((unsigned) T, T <= 16 ? (unsigned) ((H + 4) / 4) : 1u), 128, 0, c->st>>>(c->P, ldp, H, D, R, rank, L.cnorm, c->m->eps, rope, &c->d_step->st, cache, c->QK, H * (D + R), nullptr, 0);
         // absorbed queries, one product per head: QK[t][h][0..rank) = W_uk,h^T q[t][h][0..D)
         linear(c, c->P, ldp, L.ukT, c->QK, H * W, T, H, D + R, W);
     }

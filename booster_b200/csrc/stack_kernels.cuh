@@ -650,14 +650,14 @@ __device__ __forceinline__ void rope_pair(const RopeArgs & r, int pos, int i, fl
 __global__ void k_latent_prep(float * __restrict__ P, int ldp, int H, int D, int R, int rank, const float * __restrict__ cnorm, float eps,
                               RopeArgs rope, const StepState * __restrict__ st, float * __restrict__ cache, float * __restrict__ QK, int dkv_off,
                               const float * __restrict__ qnorm, int q_rank) {
-    const int t = blockIdx.x, pos = st->pos0 + t;
+    const int t = blockIdx.x, pos = st->pos0 + t, bk = blockIdx.y, nblk = gridDim.y;      // grid (T, blocks): the rotated vectors are dealt over the blocks of a token
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     float * p = P + (size_t) t * ldp;
     const float * dkv = p + dkv_off;
-    if (qnorm && warp == (nw > 1 ? 1 : 0)) warp_group_norm(p, qnorm, q_rank, eps, p, lane);
+    if (qnorm && bk == 0 && warp == (nw > 1 ? 1 : 0)) warp_group_norm(p, qnorm, q_rank, eps, p, lane);
     float * row = cache + (size_t) pos * (rank + R);
     const int half = rope.dims / 2;
-    if (warp == 0) {
+    if (warp == 0 && bk == nblk - 1) {
         float ss = 0.f;
         for (int i = lane; i < rank; i += 32) ss = fmaf(dkv[i], dkv[i], ss);
         ss = warp_sum(ss);
@@ -665,7 +665,7 @@ __global__ void k_latent_prep(float * __restrict__ P, int ldp, int H, int D, int
         for (int i = lane; i < rank; i += 32) row[i] = dkv[i] * r * cnorm[i];
     }
     // rotated vectors: index H is the shared key part, 0..H-1 the heads' query parts
-    for (int v = warp; v <= H; v += nw) {
+    for (int v = bk * nw + warp; v <= H; v += nw * nblk) {
         const float * src = v == H ? dkv + rank : p + (size_t) v * (D + R) + D;
         float * dst = v == H ? row + rank : QK + ((size_t) t * H + v) * (rank + R) + rank;
         for (int i = lane; i < R; i += 32) {

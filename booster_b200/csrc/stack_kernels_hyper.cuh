@@ -266,7 +266,10 @@ __global__ void __launch_bounds__(256) k_gqa_attn(const GqaAttnArgs a) {
     constexpr int MGW = 2 + 32 * VPL;
     float * qs = sm;                                        // [TQ][D]
     float * mg = sm + (size_t) a.TQ * a.D;                  // [8 warps][MGW]
-    const int pos0 = a.st->pos0;                            // asked for together with the queries: one round trip, not two
+    // asked for together with the queries (one round trip to memory, not one each): the step's position and the head's constants
+    const int pos0 = a.st->pos0;
+    const float r1 = a.r1 ? a.r1[h] : 0.f, r2 = a.r1 ? a.r2[h] : 0.f, snk = a.sink ? a.sink[h] : 0.f;
+    const float gate_in = a.gate && t < a.T ? a.gate[(size_t) t * a.ldg + h] : 0.f;
     for (int i = tid; i < a.TQ * a.D; i += 256) {
         const int q = i / a.D, e = i - q * a.D;
         qs[i] = t0 + q < a.T ? a.Q[(size_t) (t0 + q) * a.ldq + (size_t) h * a.D + e] : 0.f;
@@ -279,7 +282,6 @@ __global__ void __launch_bounds__(256) k_gqa_attn(const GqaAttnArgs a) {
         const int p = pos0 + t;
         const int jlo = gqa_first_token(a.mask, p), nb = gqa_blocks_seen(a.mask, p), ntot = nb + p - jlo + 1;
         const float * q1 = qs + (size_t) qi * a.D;
-        const float r1 = a.r1 ? a.r1[h] : 0.f, r2 = a.r1 ? a.r2[h] : 0.f;
         const size_t koff = (size_t) g * a.D, voff = (size_t) a.G * a.D + (size_t) g * a.V;
         const float * tokens = a.cache + ((long long) jlo - nb) * a.ldc;      // entry n >= nb is token jlo + n - nb
         for (int c = blockIdx.z * WPQ + wq; c * 32 < ntot; c += WPQ * a.nsplit) {
@@ -372,12 +374,12 @@ __global__ void __launch_bounds__(256) k_gqa_attn(const GqaAttnArgs a) {
     }
     float f = 1.0f;
     if (a.sink) {                                           // exp(sink) joins the denominator: no key, no value
-        const float snk = a.sink[h], mm = fmaxf(m, snk);
+        const float mm = fmaxf(m, snk);
         f = expf(m - mm);
         l = fmaf(l, f, expf(snk - mm));
     }
     f /= l;
-    if (a.gate) f *= sigmoidf_(a.gate[(size_t) t * a.ldg + h]);
+    if (a.gate) f *= sigmoidf_(gate_in);
 #pragma unroll
     for (int i = 0; i < VPL; i++) if (lane + 32 * i < a.V) a.A[(size_t) t * a.H * a.V + (size_t) h * a.V + lane + 32 * i] = acc[i] * f;
 }
