@@ -1080,6 +1080,10 @@ AttnPlan plan_attention(const LayerSpec & L, int n_ctx, int T, int sm_count) {
     return p;
 }
 
+bool simt_big_enabled() {
+    static const bool on = [] { const char * e = std::getenv("BOOSTER_B200_STACK_SIMT_BIG"); return !(e && e[0] == '0'); }();
+    return on;
+}
 // float32 product on the CUDA cores with explicit operand layout (the attention's two products over cached rows)
 // A second batch level (nz2 products per first-level index, strides sX2 / sW2 / sY2) serves operands that are cut twice: tiles x heads.
 void gemm_f32(StackCtx * c, const float * X, int ldx, long long sX, const float * W, int w_kn, int ldw, long long sW, float * Y, int ldy, long long sY,
@@ -1088,7 +1092,9 @@ void gemm_f32(StackCtx * c, const float * X, int ldx, long long sX, const float 
     LinArgs a{X, W, nullptr, Y, M, N, K, ldx, ldy, sX, sW, sY, 0, 0, 0.f, 0.f, w_kn, ldw, nz2, sX2, sW2, sY2};
     a.vec = K % 4 == 0 && ldx % 4 == 0 && sX % 4 == 0 && sW % 4 == 0 && sX2 % 4 == 0 && sW2 % 4 == 0 && ldw % 4 == 0 && al16(X) && al16(W);
     a.accum = accum;
-    k_gemm_simt<float><<<dim3((unsigned) ((N + 63) / 64), (unsigned) ((M + 63) / 64), (unsigned) (batch * nz2)), 256, 0, c->st>>>(a);
+    if (a.vec && M >= SG_BM && N >= SG_BN && simt_big_enabled())       // operands that fill 128 x 128 tiles
+        k_gemm_simt_big<<<dim3((unsigned) ((N + SG_BN - 1) / SG_BN), (unsigned) ((M + SG_BM - 1) / SG_BM), (unsigned) (batch * nz2)), 256, 0, c->st>>>(a);
+    else k_gemm_simt<float><<<dim3((unsigned) ((N + 63) / 64), (unsigned) ((M + 63) / 64), (unsigned) (batch * nz2)), 256, 0, c->st>>>(a);
     c->launches++;
 }
 constexpr int ATT_TQ = 16;                 // tokens per tile of the prompt attention
@@ -1425,9 +1431,8 @@ void mixer_gqattn(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) {
                               G, grp, V, (long long) Tpad * Rh * V, 1);
             c->launches++;
         }
-        k_group_o_layout<<<T, 256, 0, c->st>>>(c->OL, Tpad, H, G, V, c->A);
+        k_group_o_layout<<<T, 256, 0, c->st>>>(c->OL, Tpad, H, G, V, c->A, gate, ldp);      // the head gates ride on the regrouping
         c->launches += 2;
-        if (gate) { k_head_gate<<<T, 256, 0, c->st>>>(c->A, gate, ldp, H, V, 0); c->launches++; }
         linear(c, c->A, H * V, L.o, c->out, E, T);
         return;
     }

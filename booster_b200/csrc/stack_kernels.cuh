@@ -255,8 +255,8 @@ __global__ void __launch_bounds__(256) k_gemv(const LinArgs a) {
 // cores, 256 threads with 4 x 4 outputs each
 template <typename WT>
 __global__ void __launch_bounds__(256) k_gemm_simt(const LinArgs a) {
-    __shared__ float Xs[16][64 + 4];
-    __shared__ float Ws[16][64 + 4];
+    __shared__ __align__(16) float Xs[16][64 + 4];
+    __shared__ __align__(16) float Ws[16][64 + 4];
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
     const int z1 = blockIdx.z / a.nz2, z2 = blockIdx.z - z1 * a.nz2;
@@ -282,7 +282,17 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const LinArgs a) {
 #pragma unroll
             for (int i = 0; i < 4; i++) Xs[lk + i][lr] = v[i];
         }
-        {
+        if (a.w_kn && sizeof(WT) == 4 && a.vec) {
+            // [K][N] operand with 16-byte aligned rows: a thread takes 4 consecutive n of one k, the block one 16 x 64 tile
+            const int kk = tid >> 4, n4 = (tid & 15) * 4, k = k0 + kk, n = n0 + n4;
+            float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k < a.K && n < a.N) {
+                const float * p = reinterpret_cast<const float *>(W) + (size_t) k * a.ldw + n;
+                if (n + 3 < a.N) f = *reinterpret_cast<const float4 *>(p);
+                else { f.x = p[0]; if (n + 1 < a.N) f.y = p[1]; if (n + 2 < a.N) f.z = p[2]; }
+            }
+            *reinterpret_cast<float4 *>(&Ws[kk][n4]) = f;
+        } else {
             const int n = n0 + lr;
             float v[4] = { 0.f, 0.f, 0.f, 0.f };
             if (n < a.N) {
@@ -329,6 +339,92 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const LinArgs a) {
         for (int j = 0; j < 4; j++) {
             const int n = n0 + tx * 4 + j;
             if (n < a.N) Y[(size_t) m * a.ldy + n] = acc[i][j] + (a.bias ? a.bias[n] : 0.f) + (a.accum ? Y[(size_t) m * a.ldy + n] : 0.f);
+        }
+    }
+}
+
+// the same float32 product for operands large enough to fill 128 x 128 tiles (the attention's products over a tile of tokens x all
+// heads): 256 threads with 8 x 8 outputs each (two 4 x 4 quarters 64 apart, so that the 16-byte shared-memory reads of a
+// half-warp stay free of bank conflicts), twice the FMAs per shared-memory read of the 64 x 64 kernel, the next K slice
+// of both operands in registers while the current one is multiplied. float32 operands with 16-byte aligned rows only (a.vec);
+// plain or accumulating stores; no bias, no gated unit, no segments.
+constexpr int SG_BM = 128, SG_BN = 128, SG_BK = 16;
+__global__ void __launch_bounds__(256, 2) k_gemm_simt_big(const LinArgs a) {
+    __shared__ __align__(16) float Xs[SG_BK][SG_BM + 4];
+    __shared__ __align__(16) float Ws[SG_BK][SG_BN + 4];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * SG_BM, n0 = blockIdx.x * SG_BN;
+    const int z1 = blockIdx.z / a.nz2, z2 = blockIdx.z - z1 * a.nz2;
+    const float * X = a.X + (size_t) z1 * a.sX + (size_t) z2 * a.sX2;
+    const float * W = reinterpret_cast<const float *>(a.W) + (size_t) z1 * a.sW + (size_t) z2 * a.sW2;
+    const int ldw = a.ldw > 0 ? a.ldw : a.K;
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
+    float4 xr[2], wr[2];
+    // a K slice of both operands from global memory into registers: rows lr and lr + 64, 4 consecutive k each ([N][K] operands);
+    // a [K][N] operand: k rows kk and kk + 8, 4 consecutive n each
+    const int lr = tid >> 2, lk = (tid & 3) * 4, kk = tid >> 5, n4 = (tid & 31) * 4;
+    const auto fetch = [&](int k0) {
+        const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int m = m0 + lr + 64 * h;
+            xr[h] = zero;
+            if (m < a.T && k0 + lk < a.K) xr[h] = *reinterpret_cast<const float4 *>(X + (size_t) m * a.ldx + k0 + lk);      // K is a multiple of 4
+            wr[h] = zero;
+            if (a.w_kn) {
+                const int k = k0 + kk + 8 * h, n = n0 + n4;
+                if (k < a.K && n < a.N) {
+                    const float * p = W + (size_t) k * ldw + n;
+                    if (n + 3 < a.N) wr[h] = *reinterpret_cast<const float4 *>(p);
+                    else { wr[h].x = p[0]; if (n + 1 < a.N) wr[h].y = p[1]; if (n + 2 < a.N) wr[h].z = p[2]; }
+                }
+            } else {
+                const int n = n0 + lr + 64 * h;
+                if (n < a.N && k0 + lk < a.K) wr[h] = *reinterpret_cast<const float4 *>(W + (size_t) n * ldw + k0 + lk);
+            }
+        }
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < a.K; k0 += SG_BK) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const float xv[4] = { xr[h].x, xr[h].y, xr[h].z, xr[h].w };
+#pragma unroll
+            for (int i = 0; i < 4; i++) Xs[lk + i][lr + 64 * h] = xv[i];
+            if (a.w_kn) *reinterpret_cast<float4 *>(&Ws[kk + 8 * h][n4]) = wr[h];
+            else {
+                const float wv[4] = { wr[h].x, wr[h].y, wr[h].z, wr[h].w };
+#pragma unroll
+                for (int i = 0; i < 4; i++) Ws[lk + i][lr + 64 * h] = wv[i];
+            }
+        }
+        __syncthreads();
+        if (k0 + SG_BK < a.K) fetch(k0 + SG_BK);
+#pragma unroll
+        for (int k = 0; k < SG_BK; k++) {
+            const float4 x0 = *reinterpret_cast<const float4 *>(&Xs[k][ty * 4]), x1 = *reinterpret_cast<const float4 *>(&Xs[k][64 + ty * 4]);
+            const float4 w0 = *reinterpret_cast<const float4 *>(&Ws[k][tx * 4]), w1 = *reinterpret_cast<const float4 *>(&Ws[k][64 + tx * 4]);
+            const float xa[8] = { x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w }, wa[8] = { w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w };
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc[i][j] = fmaf(xa[i], wa[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    float * Y = a.Y + (size_t) z1 * a.sY + (size_t) z2 * a.sY2;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + i - 4);
+        if (m >= a.T) continue;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int n = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + j - 4);
+            if (n < a.N) Y[(size_t) m * a.ldy + n] = acc[i][j] + (a.accum ? Y[(size_t) m * a.ldy + n] : 0.f);
         }
     }
 }

@@ -605,12 +605,13 @@ __global__ void k_sig_weight_rows(float * __restrict__ S, int n_rows, int G, int
     const float sl = slope[h], b = pb[h];
     for (int n = lane; n < nk; n += 32) s[n] = (t < T && n <= p) ? sigmoidf_(fmaf(s[n], scale, b - sl * (float) (p - n))) : 0.f;
 }
-// Or[g][Tpad][R][V] -> A[t][h][V]
-__global__ void k_group_o_layout(const float * __restrict__ Or, int Tpad, int H, int G, int V, float * __restrict__ A) {
+// Or[g][Tpad][R][V] -> A[t][h][V], times sigmoid(gate[t][h]) when a gate is given (one number per head, rows of stride ldg)
+__global__ void k_group_o_layout(const float * __restrict__ Or, int Tpad, int H, int G, int V, float * __restrict__ A, const float * __restrict__ gate = nullptr, int ldg = 0) {
     const int t = blockIdx.x, R = H / G;
     for (int i = threadIdx.x; i < H * V; i += blockDim.x) {
         const int h = i / V, d = i - h * V, g = h / R, hq = h - g * R;
-        A[(size_t) t * H * V + i] = Or[(((size_t) g * Tpad + t) * R + hq) * V + d];
+        const float o = Or[(((size_t) g * Tpad + t) * R + hq) * V + d];
+        A[(size_t) t * H * V + i] = gate ? o * sigmoidf_(gate[(size_t) t * ldg + h]) : o;
     }
 }
 

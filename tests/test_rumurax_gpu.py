@@ -367,6 +367,19 @@ def test_a_model_without_stream_weights_is_the_plain_residual(tmp_path):
     ctx.close(); model.close()
 
 
+def test_latent_attention_over_large_tiles(tmp_path):
+    """enough heads and keys for the 128 x 128 float32 tile product of the prompt path (whole and ragged tiles in both products), beside
+    a layer that stays on the small tiles"""
+    cfg = config([latent(heads=9, dim=16, rot_dim=8, vdim=12, kv_rank=136, mlp=moe()), latent(heads=8, dim=8, rot_dim=4, vdim=8, kv_rank=128), latent(heads=3, dim=8, rot_dim=4, vdim=8, kv_rank=20)],
+                 width=64, vocab=80)
+    p = Pair(tmp_path, cfg, seed=6, n_ctx=420)
+    toks = p.tokens(410, seed=6)
+    want = p.expected(toks)
+    for cuts in (None, [128, 256, 26], [131, 1, 200, 9, 69]):
+        assert err(p.run(toks, cuts), want) < TOL32, cuts
+    p.close()
+
+
 def random_config(rng):
     """a random arrangement of the mixers with random sizes: nothing may rest on one model's values"""
     pick = lambda values: int(rng.choice(values))
@@ -386,11 +399,11 @@ def random_config(rng):
                                 cap=float(rng.choice([0.0, 3.0, 30.0])), v_mix=bool(rng.random() < 0.6), mlp=rnd_moe()))
         elif kind == 1:
             layers.append(window(heads=kv * pick([1, 2, 4]), kv_heads=kv, dim=d, vdim=pick([4, 8, 48, 128, 200]), size=pick([1, 3, 16, 50, 128]), pool=pick([0, 1, 2, 7, 16, 40]),
-                                 rot=pick([r for r in (0, 2, 4, 16, 32, 64, 128) if r <= d]), base=float(rng.choice([100.0, 1e4, 2.5e5])), scale=float(rng.choice([0.1, 0.3])),
+                                 rot=pick([r for r in (0, 2, 4, 16, 32, 64, 128) if r <= d]), base=float(rng.choice([100.0, 1e4, 5e5])), scale=float(rng.choice([0.1, 0.3])),
                                  v_mix=bool(rng.random() < 0.6), mlp=rnd_moe()))
         else:
             r = pick([0, 2, 8, 32])
-            layers.append(latent(heads=pick([1, 2, 3, 6]), dim=d, rot_dim=r, vdim=pick([4, 8, 48, 128]), kv_rank=pick([8, 24, 64, 136]), base=float(rng.choice([100.0, 2.5e5])),
+            layers.append(latent(heads=pick([1, 2, 3, 6]), dim=d, rot_dim=r, vdim=pick([4, 8, 48, 128]), kv_rank=pick([8, 24, 64, 136]), base=float(rng.choice([100.0, 5e5])),
                                  scale=float(rng.choice([0.1, 0.3])), mlp=rnd_moe()))
     # value-mixing layers must agree in kv_heads x vdim: later ones take the first one's
     first = None
